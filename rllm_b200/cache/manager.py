@@ -56,12 +56,25 @@ class PagedGroup:
         self.need, self.entries, self.block_size, self.n_blocks = need, entries, block_size, n_blocks
         self.allocator = BlockAllocator(n_blocks)
         self.pool = None                               # device tensor, see CacheManager.allocate_device
+        self.pool_k = self.pool_v = None               # in place of `pool` when value heads have a size of their own
 
     def first_needed_block(self, length: int) -> int:
-        """Logical index of the first block that tokens at positions >= length can still read."""
+        """Logical index of the first block that tokens at positions >= length can still read
+        through the window (the blocks of kept first keys come before it and stay: `kept_blocks`)."""
         if self.need.window <= 0:
             return 0
         return max(0, length + 1 - self.need.window) // RELEASE_ALIGN * RELEASE_ALIGN // self.block_size
+
+    @property
+    def kept_blocks(self) -> int:
+        """Leading blocks that are never given back: they hold the first keys that stay visible."""
+        return -(-self.need.keep_first // self.block_size) if self.need.window > 0 else 0
+
+    def planes(self, plane: int):
+        """(keys, values) of one run entry: [pages, kv_heads, block_size, head size]."""
+        if self.pool is not None:
+            return self.pool[plane, 0], self.pool[plane, 1]
+        return self.pool_k[plane], self.pool_v[plane]
 
 
 # Pages of a windowed group are given back in runs of this many keys: the attention kernels round
@@ -103,6 +116,25 @@ class CacheManager:
         self.paged: list[PagedGroup] = []
         self.stateful: list[StateGroup] = []
         self.entry_place: list = []                   # per run entry: ('kv', group, plane) | ('state', g, plane) | None
+        def place(i, need):
+            if need is None:
+                return None
+            if isinstance(need, PagedKVNeed):
+                g = next((j for j, grp in enumerate(self.paged) if grp.need == need), None)
+                if g is None:
+                    self.paged.append(PagedGroup(need, [], self._group_blocks(need, max_step_tokens), block_size))
+                    g = len(self.paged) - 1
+                self.paged[g].entries.append(i)
+                return ("kv", g, len(self.paged[g].entries) - 1)
+            if isinstance(need, StateNeed):
+                g = next((j for j, grp in enumerate(self.stateful) if grp.need == need), None)
+                if g is None:
+                    self.stateful.append(StateGroup(need, [], max_requests))
+                    g = len(self.stateful) - 1
+                self.stateful[g].entries.append(i)
+                return ("state", g, len(self.stateful[g].entries) - 1)
+            raise TypeError(f"run entry {i}: unknown cache need {need!r}")
+
         for i, need in enumerate(needs):
             owner = cache_of[i]
             if owner is not None:
@@ -113,24 +145,11 @@ class CacheManager:
                                      f"not {needs[owner]}")
                 self.entry_place.append(self.entry_place[owner])
                 continue
-            if need is None:
-                self.entry_place.append(None)
-            elif isinstance(need, PagedKVNeed):
-                g = next((j for j, grp in enumerate(self.paged) if grp.need == need), None)
-                if g is None:
-                    self.paged.append(PagedGroup(need, [], self._group_blocks(need, max_step_tokens), block_size))
-                    g = len(self.paged) - 1
-                self.paged[g].entries.append(i)
-                self.entry_place.append(("kv", g, len(self.paged[g].entries) - 1))
-            elif isinstance(need, StateNeed):
-                g = next((j for j, grp in enumerate(self.stateful) if grp.need == need), None)
-                if g is None:
-                    self.stateful.append(StateGroup(need, [], max_requests))
-                    g = len(self.stateful) - 1
-                self.stateful[g].entries.append(i)
-                self.entry_place.append(("state", g, len(self.stateful[g].entries) - 1))
+            # a mixer made of several mixers asks for several things: a tuple of needs, a tuple of places
+            if isinstance(need, (tuple, list)):
+                self.entry_place.append(tuple(place(i, nd) for nd in need))
             else:
-                raise TypeError(f"run entry {i}: unknown cache need {need!r}")
+                self.entry_place.append(place(i, need))
         self.cache_of = list(cache_of)
         self.slots = SlotAllocator(max_requests)
         self.requests: dict = {}
@@ -139,7 +158,8 @@ class CacheManager:
     def _group_blocks(self, need: PagedKVNeed, max_step_tokens) -> int:
         if need.window <= 0 or max_step_tokens is None:
             return self.n_blocks
-        per_request = -(-(need.window + int(max_step_tokens) + RELEASE_ALIGN) // self.block_size) + 1
+        per_request = (-(-(need.window + int(max_step_tokens) + RELEASE_ALIGN) // self.block_size) + 1
+                       + -(-need.keep_first // self.block_size))
         return min(self.n_blocks, self.max_requests * per_request)
 
     def set_max_length(self, n: int) -> None:
@@ -150,8 +170,14 @@ class CacheManager:
     def allocate_device(self, device, dtype) -> None:
         for grp in self.paged:
             n = grp.need
-            grp.pool = torch.zeros((len(grp.entries), 2, grp.n_blocks, n.num_kv_heads, self.block_size,
-                                    n.head_dim), dtype=dtype, device=device)
+            if n.value_dim == n.head_dim:
+                grp.pool = torch.zeros((len(grp.entries), 2, grp.n_blocks, n.num_kv_heads, self.block_size,
+                                        n.head_dim), dtype=dtype, device=device)
+            else:
+                grp.pool_k = torch.zeros((len(grp.entries), grp.n_blocks, n.num_kv_heads, self.block_size,
+                                          n.head_dim), dtype=dtype, device=device)
+                grp.pool_v = torch.zeros((len(grp.entries), grp.n_blocks, n.num_kv_heads, self.block_size,
+                                          n.value_dim), dtype=dtype, device=device)
         for grp in self.stateful:
             # one slot more than requests: the last one belongs to nobody; the padding rows of a step
             # that is replayed from a CUDA graph read and write it
@@ -161,15 +187,16 @@ class CacheManager:
     def device_bytes(self) -> int:
         total = 0
         for grp in self.paged:
-            if grp.pool is not None:
-                total += grp.pool.numel() * grp.pool.element_size()
+            for pool in (grp.pool, grp.pool_k, grp.pool_v):
+                if pool is not None:
+                    total += pool.numel() * pool.element_size()
         for grp in self.stateful:
             if grp.state is not None:
                 total += grp.state.numel() * grp.state.element_size()
         return total
 
     def bytes_per_token(self, element_size: int) -> int:
-        return sum(2 * len(g.entries) * g.need.num_kv_heads * g.need.head_dim * element_size
+        return sum(len(g.entries) * g.need.num_kv_heads * (g.need.head_dim + g.need.value_dim) * element_size
                    for g in self.paged)
 
     # ------------------------------------------------------------------ requests
@@ -269,7 +296,7 @@ class CacheManager:
         for gi, grp in enumerate(self.paged):
             first = grp.first_needed_block(req.length)
             table = req.tables[gi]
-            for b in range(min(first, len(table))):
+            for b in range(grp.kept_blocks, min(first, len(table))):
                 if table[b] is not None:
                     grp.allocator.release(table[b])
                     table[b] = None

@@ -33,6 +33,7 @@ def host_lib():
         lib.rllm_cache_create.restype = c_void_p
         lib.rllm_cache_create.argtypes = [c_int, POINTER(c_int), c_int, c_int, c_int, POINTER(c_int)]
         lib.rllm_cache_destroy.argtypes = [c_void_p]
+        lib.rllm_cache_set_keep_first.argtypes = [c_void_p, c_int, c_int]
         for name in ("has", "length", "state_slot"):
             getattr(lib, f"rllm_cache_{name}").argtypes = [c_void_p, c_int64]
         lib.rllm_cache_n_requests.argtypes = [c_void_p]
@@ -82,6 +83,9 @@ class NativeCacheManager(CacheManager):
                                                  group_blocks))
         if not self._h:
             raise ValueError("cache manager: bad sizes")
+        for g, grp in enumerate(self.paged):
+            if grp.need.keep_first and lib.rllm_cache_set_keep_first(self._h, g, grp.need.keep_first):
+                raise ValueError("cache manager: bad number of kept first keys")
         self._ids: dict = {}
         self._next = 1
         self.slots = _Slots(self)

@@ -35,18 +35,24 @@ class LayerSpec:
     the position encoding handed to the mixer (None: the mixer uses none)."""
     block: str
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]          # None: the layer has no feed-forward sublayer
     norms: Mapping[str, PartSpec]
     position: Optional[PartSpec] = None
+    block_params: Mapping[str, Any] = field(default_factory=dict)    # constants of the arrangement itself
 
 
 @dataclass(frozen=True)
 class RunEntry:
     """One entry of the run order: which layer runs, and whose cache its mixer uses.
     `cache_of` is the index of an EARLIER run entry whose cache this one reads without
-    writing (None: the entry owns a cache of its own and writes it)."""
+    writing (None: the entry owns a cache of its own and writes it).  `junction`: index into
+    the model's `junctions` of a part that rewrites the residual stream right before this entry
+    (it also sees the embedding output), called with `junction_arg` (e.g. the number of the pass
+    through a block of layers that this entry opens)."""
     layer: int
     cache_of: Optional[int] = None
+    junction: Optional[int] = None
+    junction_arg: int = 0
 
 
 @dataclass(frozen=True)
@@ -59,7 +65,9 @@ class ModelSpec:
     run_order: tuple         # of RunEntry; may name a layer twice
     final_norm: PartSpec
     lm_head: PartSpec
-    max_position: int
+    max_position: int                # 0: the model sets no limit
+    junctions: tuple = ()            # of PartSpec (category 'junction'); run entries name them
+    residual_scale: float = 1.0      # what a sublayer's output is multiplied by when it joins the residual stream
 
 
 def require(d: Mapping[str, Any], key: str, typ, where: str = "config.json"):

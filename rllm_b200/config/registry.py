@@ -32,8 +32,11 @@ def config_class(name: str) -> Type[ModelConfig]:
 
 def config_from_dict(d: Mapping[str, Any]) -> ModelConfig:
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]                      # some families give one name instead of a list
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: required key 'architectures' is missing or not a list of names")
+        raise ConfigError("config.json: required key 'architectures' (a list of names) or 'architecture' "
+                          "(one name) is missing")
     return config_class(archs[0]).from_dict(d)
 
 

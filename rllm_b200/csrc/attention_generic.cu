@@ -4,9 +4,12 @@
 // the engine and the reference the tensor-core kernels are tested against.
 //
 // Token t of request r = seq_ids[t] at absolute position pos sees keys p with
-// max(0, pos+1-window) <= p <= pos (window 0: all keys); the keys of the step's own
+// max(0, pos+1-window) <= p <= pos (window 0: all keys) and, with keep_first > 0, also the
+// keys p < keep_first that the window has left behind (they keep their positions; a model
+// without position encoding in the scores sees no difference).  The keys of the step's own
 // tokens are already in the cache.  Key p lives in page block_table[r][p / bs] at
-// offset p % bs; cache layout [page][kv_head][bs][hd].
+// offset p % bs; cache layouts [page][kv_head][bs][hd] for keys and [page][kv_head][bs][hdv]
+// for values (the value heads may have another size; the output is [n, H * hdv]).
 //
 // Formula: crates/rllm-cpu/src/lib.rs:389-425 of AxiomOperator/rllm; its device
 // counterpart is paged_attention (crates/rllm-cuda/kernels/kernels.cu:1634-1690).
@@ -24,7 +27,8 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
                                const TC* v_cache, TO* out,
                                const int* __restrict__ positions, const int* __restrict__ seq_ids,
                                const int* __restrict__ block_table, int table_stride, int H, int K,
-                               int hd, int bs, float scale, int window, int n_pages, int* err) {
+                               int hd, int hdv, int bs, float scale, int window, int keep_first, int n_pages,
+                               int* err) {
     extern __shared__ float smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -49,10 +53,14 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
     for (int a = 0; a < ATT_MAX_ACC; ++a) acc[a] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
 
-    for (int c0 = first; c0 <= pos; c0 += ATT_THREADS) {
+    // two runs of keys: the kept first ones outside the window, then the window
+    const int kept = keep_first < first ? keep_first : first;
+    for (int run = 0; run < 2; ++run) {
+    const int lo = run == 0 ? 0 : first, hi = run == 0 ? kept : pos + 1;
+    for (int c0 = lo; c0 < hi; c0 += ATT_THREADS) {
         const int p = c0 + tid;
         float s = -INFINITY;
-        if (p <= pos) {
+        if (p < hi) {
             int page = table[p / bs];
             if (page < 0 || page >= n_pages) {        // refused: read page 0, report
                 if (err) atomicExch(err, RLLM_ERR_PAGE);
@@ -67,30 +75,31 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
         }
         const float cmax = block_max(s, red);
         const float m_new = fmaxf(m_run, cmax);
-        const float e = (p <= pos) ? expf(s - m_new) : 0.f;
+        const float e = (p < hi) ? expf(s - m_new) : 0.f;
         pr[tid] = e;
         const float csum = block_sum(e, red);          // also orders pr/rowoff writes before reads
         const float alpha = (m_run == -INFINITY) ? 0.f : expf(m_run - m_new);
         l_run = l_run * alpha + csum;
         m_run = m_new;
-        const int cn = min(ATT_THREADS, pos + 1 - c0);
+        const int cn = min(ATT_THREADS, hi - c0);
 #pragma unroll
         for (int a = 0; a < ATT_MAX_ACC; ++a) {
             const int d = tid + a * ATT_THREADS;
-            if (d < hd) {
+            if (d < hdv) {
                 float v = acc[a] * alpha;
-                for (int j = 0; j < cn; ++j) v += pr[j] * to_f<TC>(v_cache[(size_t)rowoff[j] * hd + d]);
+                for (int j = 0; j < cn; ++j) v += pr[j] * to_f<TC>(v_cache[(size_t)rowoff[j] * hdv + d]);
                 acc[a] = v;
             }
         }
         __syncthreads();
     }
-    TO* orow = out + ((size_t)t * H + h) * hd;
+    }
+    TO* orow = out + ((size_t)t * H + h) * hdv;
     const float inv = 1.0f / l_run;
 #pragma unroll
     for (int a = 0; a < ATT_MAX_ACC; ++a) {
         const int d = tid + a * ATT_THREADS;
-        if (d < hd) orow[d] = from_f<TO>(acc[a] * inv);
+        if (d < hdv) orow[d] = from_f<TO>(acc[a] * inv);
     }
 }
 
@@ -98,20 +107,23 @@ RLLM_API int rllm_paged_attention_generic(const void* q, int q_dtype, const void
                                           const void* v_cache, int cache_dtype, void* out,
                                           int out_dtype, const int* positions, const int* seq_ids,
                                           const int* block_table, int table_stride, int n, int H,
-                                          int K, int hd, int bs, float scale, int window, int n_pages, int* err,
-                                          cudaStream_t stream) {
+                                          int K, int hd, int hdv, int bs, float scale, int window, int keep_first,
+                                          int n_pages, int* err, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (hd > ATT_THREADS * ATT_MAX_ACC || K <= 0 || H % K != 0 || bs <= 0) return (int)cudaErrorInvalidValue;
+    if (hd > ATT_THREADS * ATT_MAX_ACC || hdv > ATT_THREADS * ATT_MAX_ACC || hdv <= 0 || K <= 0 || H % K != 0 ||
+        bs <= 0 || keep_first < 0)
+        return (int)cudaErrorInvalidValue;
     if (q_dtype != cache_dtype || q_dtype != out_dtype) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(hd + 2 * ATT_THREADS) * sizeof(float);
     dim3 grid(n, H);
     if (q_dtype == RLLM_F32)
         return rllm_launch(paged_attention_generic_kernel<float, float, float>, grid, dim3(ATT_THREADS), smem,
                            stream, (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out,
-                           positions, seq_ids, block_table, table_stride, H, K, hd, bs, scale, window, n_pages, err);
+                           positions, seq_ids, block_table, table_stride, H, K, hd, hdv, bs, scale, window, keep_first, n_pages,
+                           err);
     return rllm_launch(paged_attention_generic_kernel<bf16, bf16, bf16>, grid, dim3(ATT_THREADS), smem, stream,
                        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions,
-                       seq_ids, block_table, table_stride, H, K, hd, bs, scale, window, n_pages, err);
+                       seq_ids, block_table, table_stride, H, K, hd, hdv, bs, scale, window, keep_first, n_pages, err);
 }
 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches

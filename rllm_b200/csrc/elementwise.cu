@@ -44,7 +44,7 @@ RLLM_API int rllm_embed(const void* table, int table_dtype, const int* tokens, f
 template <typename TD, typename TO>
 __global__ void add_rms_norm_kernel(float* x, const TD* delta,
                                     const int* __restrict__ rows, const float* __restrict__ w,
-                                    TO* __restrict__ out, int d, float eps, int write_x) {
+                                    TO* __restrict__ out, int d, float eps, int write_x, float delta_scale) {
     __shared__ float red[33];
     pdl_launch_dependents();          // the product that follows fetches its first weights beside this kernel
     pdl_wait();
@@ -57,7 +57,7 @@ __global__ void add_rms_norm_kernel(float* x, const TD* delta,
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = xr[i];
         if (dr) {
-            v += to_f<TD>(dr[i]);
+            v += delta_scale * to_f<TD>(dr[i]);
             if (write_x) xr[i] = v;
         }
         ss += v * v;
@@ -67,7 +67,7 @@ __global__ void add_rms_norm_kernel(float* x, const TD* delta,
     TO* o = out + (size_t)r * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = xr[i];
-        if (dr && !write_x) v += to_f<TD>(dr[i]);
+        if (dr && !write_x) v += delta_scale * to_f<TD>(dr[i]);
         o[i] = from_f<TO>(v * rs * w[i]);
     }
 }
@@ -90,7 +90,8 @@ template <> __device__ __forceinline__ void store2<bf16>(bf16* p, float a, float
 template <typename TD, typename TO, int NV>
 __global__ void __launch_bounds__(256)
 add_rms_norm_vec_kernel(float* x, const TD* delta, const int* __restrict__ rows,
-                        const float* __restrict__ w, TO* __restrict__ out, int d, float eps, int write_x) {
+                        const float* __restrict__ w, TO* __restrict__ out, int d, float eps, int write_x,
+                        float delta_scale) {
     __shared__ float red[33];
     pdl_launch_dependents();          // as above
     pdl_wait();
@@ -107,8 +108,8 @@ add_rms_norm_vec_kernel(float* x, const TD* delta, const int* __restrict__ rows,
         if (i < d) {
             v[it] = *reinterpret_cast<const float4*>(xr + i);
             if (dr) {
-                v[it].x += to_f<TD>(dr[i]); v[it].y += to_f<TD>(dr[i + 1]);
-                v[it].z += to_f<TD>(dr[i + 2]); v[it].w += to_f<TD>(dr[i + 3]);
+                v[it].x += delta_scale * to_f<TD>(dr[i]); v[it].y += delta_scale * to_f<TD>(dr[i + 1]);
+                v[it].z += delta_scale * to_f<TD>(dr[i + 2]); v[it].w += delta_scale * to_f<TD>(dr[i + 3]);
                 if (write_x) *reinterpret_cast<float4*>(xr + i) = v[it];
             }
             ss += v[it].x * v[it].x + v[it].y * v[it].y + v[it].z * v[it].z + v[it].w * v[it].w;
@@ -130,11 +131,11 @@ add_rms_norm_vec_kernel(float* x, const TD* delta, const int* __restrict__ rows,
 
 template <typename TD, typename TO>
 static int launch_norm(float* x, const void* delta, const int* rows, const float* w, void* out, int n_rows, int d,
-                       float eps, int write_x, cudaStream_t stream) {
+                       float eps, int write_x, float delta_scale, cudaStream_t stream) {
     const bool vec = d % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
 #define VEC(NV)                                                                                        \
     return rllm_launch(add_rms_norm_vec_kernel<TD, TO, NV>, dim3(n_rows), dim3(256), 0, stream, x,     \
-                       (const TD*)delta, rows, w, (TO*)out, d, eps, write_x)
+                       (const TD*)delta, rows, w, (TO*)out, d, eps, write_x, delta_scale)
     if (vec && d <= 1024) VEC(1);
     if (vec && d <= 2048) VEC(2);
     if (vec && d <= 4096) VEC(4);
@@ -143,20 +144,20 @@ static int launch_norm(float* x, const void* delta, const int* rows, const float
     int threads = 32;
     while (threads < d / 4 && threads < 1024) threads <<= 1;
     return rllm_launch(add_rms_norm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, x, (const TD*)delta,
-                       rows, w, (TO*)out, d, eps, write_x);
+                       rows, w, (TO*)out, d, eps, write_x, delta_scale);
 }
 
 RLLM_API int rllm_add_rms_norm(float* x, const void* delta, int delta_dtype, const int* rows,
                                const float* w, void* out, int out_dtype, int n_rows, int d,
-                               float eps, int write_x, cudaStream_t stream) {
+                               float eps, int write_x, float delta_scale, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (delta_dtype == RLLM_F32 && out_dtype == RLLM_F32)
-        return launch_norm<float, float>(x, delta, rows, w, out, n_rows, d, eps, write_x, stream);
+        return launch_norm<float, float>(x, delta, rows, w, out, n_rows, d, eps, write_x, delta_scale, stream);
     if (delta_dtype == RLLM_F32 && out_dtype == RLLM_BF16)
-        return launch_norm<float, bf16>(x, delta, rows, w, out, n_rows, d, eps, write_x, stream);
+        return launch_norm<float, bf16>(x, delta, rows, w, out, n_rows, d, eps, write_x, delta_scale, stream);
     if (delta_dtype == RLLM_BF16 && out_dtype == RLLM_F32)
-        return launch_norm<bf16, float>(x, delta, rows, w, out, n_rows, d, eps, write_x, stream);
-    return launch_norm<bf16, bf16>(x, delta, rows, w, out, n_rows, d, eps, write_x, stream);
+        return launch_norm<bf16, float>(x, delta, rows, w, out, n_rows, d, eps, write_x, delta_scale, stream);
+    return launch_norm<bf16, bf16>(x, delta, rows, w, out, n_rows, d, eps, write_x, delta_scale, stream);
 }
 
 // Plain residual add x += delta (used after the last layer when no norm follows).

@@ -47,6 +47,7 @@ struct Request {
 
 struct Group {
     int window;
+    int keep_first = 0;              // the first keys of a request that stay readable behind the window
     Allocator alloc;
     int n_blocks;                    // pages of this group's pool
     Group(int w, int nb) : window(w), alloc(nb), n_blocks(nb) {}
@@ -150,7 +151,8 @@ struct Cache {
             if (groups[g].window <= 0) continue;
             const int first = std::max(0, it->second.length + 1 - groups[g].window) / RELEASE_ALIGN * RELEASE_ALIGN / block_size;
             auto& table = it->second.tables[g];
-            for (int b = 0; b < std::min(first, (int)table.size()); ++b)
+            const int kept = (groups[g].keep_first + block_size - 1) / block_size;   // blocks of the kept first keys stay
+            for (int b = kept; b < std::min(first, (int)table.size()); ++b)
                 if (table[b] >= 0) {
                     if (!groups[g].alloc.release(table[b])) return ERR_DOUBLE_FREE;
                     table[b] = -1;
@@ -219,6 +221,12 @@ API void* rllm_cache_create(int n_groups, const int* windows, int block_size, in
     return new Cache(n_groups, windows, block_size, n_blocks, max_requests, group_blocks);
 }
 API void rllm_cache_destroy(void* c) { delete static_cast<Cache*>(c); }
+API int rllm_cache_set_keep_first(void* c, int group, int n) {
+    auto* cache = static_cast<Cache*>(c);
+    if (group < 0 || group >= (int)cache->groups.size() || n < 0) return ERR_BAD_ARG;
+    cache->groups[group].keep_first = n;
+    return OK;
+}
 API int rllm_cache_has(void* c, int64_t rid) { return (int)static_cast<Cache*>(c)->requests.count(rid); }
 API int rllm_cache_length(void* c, int64_t rid) {
     auto& r = static_cast<Cache*>(c)->requests;

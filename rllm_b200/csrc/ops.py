@@ -256,9 +256,9 @@ def embed(table, tokens, out, err=None):
     return out
 
 
-def add_rms_norm(x, delta, weight, out, eps, rows=None, write_x=True):
-    """out[r] = rmsnorm(x[src] (+ delta[src])) * weight with src = rows[r] if rows is given else r.
-    x is the float32 residual stream and receives the sum when write_x (and delta is given)."""
+def add_rms_norm(x, delta, weight, out, eps, rows=None, write_x=True, delta_scale=1.0):
+    """out[r] = rmsnorm(x[src] (+ delta_scale * delta[src])) * weight with src = rows[r] if rows is given
+    else r.  x is the float32 residual stream and receives the sum when write_x (and delta is given)."""
     _need_cuda(x, delta, weight, out, rows)
     _need_contig(x=x, delta=delta, weight=weight, out=out, rows=rows)
     d = x.shape[-1]
@@ -273,7 +273,8 @@ def add_rms_norm(x, delta, weight, out, eps, rows=None, write_x=True):
         assert delta.shape == x.shape
     _check(core().rllm_add_rms_norm(_ptr(x), _ptr(delta), c_int(_code(delta) if delta is not None else F32),
                                     _ptr(rows), _ptr(weight), _ptr(out), c_int(_code(out)), c_int(n_rows),
-                                    c_int(d), c_float(eps), c_int(1 if write_x else 0), _stream()),
+                                    c_int(d), c_float(eps), c_int(1 if write_x else 0), c_float(delta_scale),
+                                    _stream()),
            "add_rms_norm")
     return out
 
@@ -343,23 +344,188 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, q_ou
 # ------------------------------------------------------------------ attention
 
 def paged_attention_generic(q, k_cache, v_cache, out, positions, seq_ids, block_table, H, K, hd,
-                            block_size, scale, window=0):
-    """Plain paged causal attention; q/out [n, H*hd], caches [pages, K, block_size, hd]."""
+                            block_size, scale, window=0, keep_first=0, v_head_dim=None):
+    """Plain paged causal attention; q [n, H*hd], out [n, H*hdv], caches [pages, K, block_size, hd] and
+    [pages, K, block_size, hdv] (hdv = v_head_dim, hd by default).  keep_first: the first keys of a
+    request stay visible when the window has passed them."""
     _need_cuda(q, k_cache, v_cache, out, positions, seq_ids, block_table)
     _need_contig(q=q, k_cache=k_cache, v_cache=v_cache, out=out, positions=positions, seq_ids=seq_ids)
     n = q.shape[0]
-    assert q.shape == (n, H * hd) and out.shape == (n, H * hd)
+    hdv = hd if not v_head_dim else int(v_head_dim)
+    assert q.shape == (n, H * hd) and out.shape == (n, H * hdv)
+    assert k_cache.shape[-1] == hd and v_cache.shape[-1] == hdv
     assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.stride(1) == 1
     assert positions.dtype == torch.int32 and seq_ids.dtype == torch.int32
-    if hd > 512:
-        raise KernelError(f"head size {hd} exceeds the attention kernel's limit of 512")
+    if hd > 512 or hdv > 512:
+        raise KernelError(f"head size {max(hd, hdv)} exceeds the attention kernel's limit of 512")
     if H % K:
         raise KernelError(f"{H} query heads are not a multiple of {K} key/value heads")
     _check(core().rllm_paged_attention_generic(
         _ptr(q), c_int(_code(q)), _ptr(k_cache), _ptr(v_cache), c_int(_code(k_cache)), _ptr(out),
         c_int(_code(out)), _ptr(positions), _ptr(seq_ids), _ptr(block_table), c_int(block_table.stride(0)),
-        c_int(n), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale), c_int(window),
-        c_int(min(k_cache.shape[0], 0x7fffffff)), _ptr(error_word(q.device)), _stream()), "paged_attention_generic")
+        c_int(n), c_int(H), c_int(K), c_int(hd), c_int(hdv), c_int(block_size), c_float(scale), c_int(window),
+        c_int(keep_first), c_int(min(k_cache.shape[0], 0x7fffffff)), _ptr(error_word(q.device)), _stream()),
+        "paged_attention_generic")
+    return out
+
+
+# ------------------------------------------------------------------ row-wise helpers (rowwise.cu)
+
+ACT = {None: 0, "none": 0, "silu": 1, "relu2": 2, "sigmoid": 3, "tanh": 4, "softplus": 5}
+
+
+def _rows2d(t, name):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be a matrix whose rows are contiguous")
+    return t
+
+
+def rows_act(a, out, act=None, bias=None, mul=None, mul_act=None):
+    """out[t, c] = f(a[t, c] + bias[c]) * g(mul[t, c]); a, mul, out may be column slices of wider
+    matrices (any row stride), float32 or bfloat16; bias float32.  f, g by name (ACT)."""
+    _need_cuda(a, out, bias, mul)
+    _rows2d(a, "a"), _rows2d(out, "out")
+    n, cols = out.shape
+    assert a.shape == (n, cols) and (mul is None or _rows2d(mul, "mul").shape == (n, cols))
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == cols and bias.is_contiguous())
+    _check(core().rllm_rows_act(_ptr(a), c_int(_code(a)), c_longlong(a.stride(0)), _ptr(bias), c_int(ACT[act]),
+                                _ptr(mul), c_int(_code(mul) if mul is not None else F32),
+                                c_longlong(mul.stride(0) if mul is not None else 0), c_int(ACT[mul_act]), _ptr(out),
+                                c_int(_code(out)), c_longlong(out.stride(0)), c_int(n), c_int(cols), _stream()),
+           "rows_act")
+    return out
+
+
+def axpby(a, x, b, y, out):
+    """out = a * x + b * y over float32 tensors of one shape."""
+    _need_cuda(x, y, out)
+    _need_contig(x=x, y=y, out=out)
+    assert x.dtype == y.dtype == out.dtype == torch.float32 and x.shape == y.shape == out.shape
+    _check(core().rllm_axpby(c_float(a), _ptr(x), c_float(b), _ptr(y), _ptr(out), c_longlong(out.numel()),
+                             _stream()), "axpby")
+    return out
+
+
+def cat2_cast(x, y, out, delta=None, delta_scale=1.0):
+    """out[t] = [x[t] + delta_scale * delta[t] | y[t]]; x, y float32 [n, d], out [n, 2d]."""
+    _need_cuda(x, y, out, delta)
+    _need_contig(x=x, y=y, out=out, delta=delta)
+    n, d = x.shape
+    assert x.dtype == y.dtype == torch.float32 and y.shape == (n, d) and out.shape == (n, 2 * d)
+    assert delta is None or delta.shape == (n, d)
+    _check(core().rllm_cat2_cast(_ptr(x), _ptr(delta), c_int(_code(delta) if delta is not None else F32),
+                                 c_float(delta_scale), _ptr(y), _ptr(out), c_int(_code(out)), c_int(n), c_int(d),
+                                 _stream()), "cat2_cast")
+    return out
+
+
+def qkv_rownorm_store(qkv, bias, q_norm_w, k_norm_w, slots, q_out, k_cache, v_cache, H, G, dk, dv, block_size, eps,
+                      write_kv=True):
+    """Biased q/k/v row -> RMSNorm over the whole q row and the whole k row (weights per column, None:
+    no norm) -> queries out, keys and values into the paged cache; see rowwise.cu."""
+    _need_cuda(qkv, bias, q_norm_w, k_norm_w, slots, q_out, k_cache, v_cache)
+    _need_contig(qkv=qkv, q_out=q_out, k_cache=k_cache, v_cache=v_cache, slots=slots)
+    n = qkv.shape[0]
+    assert qkv.shape[1] == H * dk + G * dk + G * dv and q_out.shape == (n, H * dk)
+    assert slots.dtype == torch.int32 and slots.numel() == n
+    assert k_cache.shape[1:] == (G, block_size, dk) and v_cache.shape[1:] == (G, block_size, dv)
+    assert k_cache.dtype == v_cache.dtype == q_out.dtype
+    for w, size in ((bias, qkv.shape[1]), (q_norm_w, H * dk), (k_norm_w, G * dk)):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == size and w.is_contiguous())
+    _check(core().rllm_qkv_rownorm_store(
+        _ptr(qkv), c_int(_code(qkv)), _ptr(bias), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(slots), _ptr(q_out),
+        _ptr(k_cache), _ptr(v_cache), c_int(_code(q_out)), c_int(n), c_int(H), c_int(G), c_int(dk), c_int(dv),
+        c_int(block_size), c_float(eps), c_int(1 if write_kv else 0), c_longlong(k_cache.shape[0] * block_size),
+        _ptr(error_word(qkv.device)), _stream()), "qkv_rownorm_store")
+    return q_out
+
+
+# ------------------------------------------------------------------ layers with a state per request (recurrent.cu)
+
+def _state2d(state):
+    """The plane of state slots as [slots, floats per slot]."""
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2
+    return state
+
+
+def conv_silu(xz, weight, bias, state, conv_off, ctx_seq_ids, cu_q, slots, out, inner):
+    """Causal per-channel convolution + silu over columns [0, inner) of xz (float32), reaching back into
+    the request's kept inputs at state[slot, conv_off:]; weight [inner, taps] float32."""
+    _need_cuda(xz, weight, bias, state, out)
+    _rows2d(xz, "xz"), _need_contig(out=out, weight=weight)
+    n = xz.shape[0]
+    taps = weight.shape[1]
+    assert xz.dtype == weight.dtype == torch.float32 and weight.shape[0] == inner and out.shape == (n, inner)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == inner)
+    st = _state2d(state)
+    assert conv_off + inner * (taps - 1) <= st.shape[1]
+    _check(_lib("recur").rllm_conv_silu(_ptr(xz), c_longlong(xz.stride(0)), _ptr(weight), _ptr(bias), _ptr(st),
+                                        c_longlong(st.stride(0)), c_longlong(conv_off), _ptr(ctx_seq_ids), _ptr(cu_q),
+                                        _ptr(slots), _ptr(out), c_int(_code(out)), c_int(n), c_int(inner), c_int(taps),
+                                        _stream()), "conv_silu")
+    return out
+
+
+def selective_scan(x, xz, low, b_off, c_off, dtr, dt_bias, A, D, state, conv_off, cu_q, slots, out, n_requests,
+                   inner, N, taps):
+    """The selective scan over each request's tokens with its state in state[slot, :inner*N]; see
+    recurrent.cu.  x, out: activation type [n, inner]; xz, low, dtr float32."""
+    _need_cuda(x, xz, low, dtr, dt_bias, A, D, state, out)
+    _need_contig(x=x, out=out, dtr=dtr, A=A)
+    _rows2d(xz, "xz"), _rows2d(low, "low")
+    n = x.shape[0]
+    assert x.dtype == out.dtype and x.shape == out.shape == (n, inner) and dtr.shape == (n, inner)
+    assert xz.dtype == low.dtype == dtr.dtype == torch.float32 and xz.shape[1] >= 2 * inner
+    assert A.shape == (inner, N) and A.dtype == dt_bias.dtype == D.dtype == torch.float32
+    assert dt_bias.numel() == inner and D.numel() == inner and max(b_off, c_off) + N <= low.shape[1]
+    st = _state2d(state)
+    assert conv_off >= inner * N and conv_off + inner * (taps - 1) <= st.shape[1]
+    if N > 256:
+        raise KernelError(f"state size {N} exceeds the scan kernel's limit of 256")
+    _check(_lib("recur").rllm_selective_scan(
+        _ptr(x), c_int(_code(x)), _ptr(xz), c_longlong(xz.stride(0)), _ptr(low), c_longlong(low.stride(0)),
+        c_int(b_off), c_int(c_off), _ptr(dtr), _ptr(dt_bias), _ptr(A), _ptr(D), _ptr(st), c_longlong(st.stride(0)),
+        c_longlong(conv_off), _ptr(cu_q), _ptr(slots), _ptr(out), c_int(n_requests), c_int(inner), c_int(N),
+        c_int(taps), _stream()), "selective_scan")
+    return out
+
+
+def token_shift(h, mu, state, prev_off, seq_ids, cu_q, slots, out):
+    """out[s] = h + (previous row - h) * mu[s]; mu float32 [streams, d], out [streams, n, d]; the row
+    before a request's first token of the step is state[slot, prev_off:prev_off + d]."""
+    _need_cuda(h, mu, state, out)
+    _need_contig(h=h, mu=mu, out=out)
+    n, d = h.shape
+    S = mu.shape[0]
+    assert mu.dtype == torch.float32 and mu.shape == (S, d) and out.shape == (S, n, d) and out.dtype == h.dtype
+    st = _state2d(state)
+    assert prev_off + d <= st.shape[1]
+    _check(_lib("recur").rllm_token_shift(_ptr(h), c_int(_code(h)), _ptr(mu), _ptr(st), c_longlong(st.stride(0)),
+                                          c_longlong(prev_off), _ptr(seq_ids), _ptr(cu_q), _ptr(slots), _ptr(out),
+                                          c_int(n), c_int(d), c_int(S), _stream()), "token_shift")
+    return out
+
+
+def wkv(r, k, v, wraw, g, w0, u, norm_w, eps, state, prev_off, h, cu_q, slots, out, n_requests, H, D):
+    """The RWKV recurrence with data-dependent decay, unit norm per head, norm weight and silu gate; see
+    recurrent.cu.  r, k, v, wraw, g float32 [n, H*D] (equal row strides); out activation type."""
+    _need_cuda(r, k, v, wraw, g, w0, u, norm_w, state, h, out)
+    n = out.shape[0]
+    for name, t in (("r", r), ("k", k), ("v", v), ("wraw", wraw), ("g", g)):
+        _rows2d(t, name)
+        assert t.dtype == torch.float32 and t.shape == (n, H * D) and t.stride(0) == r.stride(0)
+    _need_contig(out=out, h=h, w0=w0, u=u, norm_w=norm_w)
+    assert out.shape == (n, H * D) and h.dtype == out.dtype and h.shape[0] == n
+    assert w0.dtype == u.dtype == norm_w.dtype == torch.float32
+    assert w0.numel() == u.numel() == norm_w.numel() == H * D
+    if D > 256:
+        raise KernelError(f"head size {D} exceeds the WKV kernel's limit of 256")
+    st = _state2d(state)
+    assert prev_off >= H * D * D and prev_off + h.shape[1] <= st.shape[1]
+    _check(_lib("recur").rllm_wkv(_ptr(r), _ptr(k), _ptr(v), _ptr(wraw), _ptr(g), c_longlong(r.stride(0)), _ptr(w0),
+                                  _ptr(u), _ptr(norm_w), c_float(eps), _ptr(st), c_longlong(st.stride(0)),
+                                  c_longlong(prev_off), _ptr(h), c_int(_code(h)), c_int(h.shape[1]), _ptr(cu_q),
+                                  _ptr(slots), _ptr(out), c_int(n_requests), c_int(H), c_int(D), _stream()), "wkv")
     return out
 
 
@@ -1045,13 +1211,16 @@ def attention_tc(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_re
     return out
 
 
-def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_size, scale, window=0):
+def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_size, scale, window=0,
+                    keep_first=0, v_head_dim=None):
     """Attention of the step's tokens over the paged cache; chooses the kernel by element type,
-    head size and the shape of the step (`ctx`: the step's StepContext).  float32, and head sizes
-    other than 64 and 128, take the plain kernel."""
-    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS:
+    head size and the shape of the step (`ctx`: the step's StepContext).  float32, head sizes
+    other than 64 and 128, value heads of another size than the key heads and windows that keep
+    the first keys take the plain kernel."""
+    hdv = hd if not v_head_dim else int(v_head_dim)
+    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd or (keep_first and window):
         return paged_attention_generic(q, k_cache, v_cache, out, ctx.positions, ctx.seq_ids, block_table,
-                                       H, K, hd, block_size, scale, window)
+                                       H, K, hd, block_size, scale, window, keep_first, hdv)
     key = (H // K, window)
     plan = ctx.plans.get(key)
     if plan is None:

@@ -1,0 +1,327 @@
+// Layers that carry a fixed-size state per request from token to token: the selective scan
+// (Mamba) with its short causal convolution, and RWKV-style time mixing with a data-dependent
+// decay.  A request's state lives in a slot of the state array (float32), is read at the start of
+// the request's tokens in this step and written back at their end; the tokens of a request are
+// contiguous in the flat batch (cu_q) and in order.  Everything that enters a recurrence (step
+// sizes, decays, their exponentials, gates, unit norms, the state itself) is float32 with accurate
+// expf / log1pf; one thread (or a fixed group of lanes) owns a state element for the whole step,
+// and sums run in a fixed order, so a request's result does not depend on what else is in the
+// batch, on how its tokens were cut into steps, or on the slot it has.
+//
+// State slot layouts (floats):
+//   Mamba:  S [inner][N], then the last taps-1 inputs of the convolution [inner][taps-1] (oldest first)
+//   RWKV :  S [heads][D (key channel)][D (value channel)], then the previous token's input [width]
+#include "common.cuh"
+#include <math.h>
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// ------------------------------------------------------------------ causal convolution + silu
+// xz [n, ld] float32 holds the convolution's input in columns [0, inner).  Token t (index i in
+// its request's portion) and channel c:
+//   out[t, c] = silu(b[c] + sum_j w[c, j] * in(i - (taps-1) + j)),  in(i') = xz row of that token
+//   for i' >= 0, else the request's kept inputs (state) -- zeros at the start of a sequence.
+// The state itself is advanced by the scan kernel, which runs after every read here.
+template <typename TO>
+__global__ void conv_silu_kernel(const float* xz, long long ld, const float* __restrict__ w,
+                                 const float* __restrict__ b, const float* state, long long slot_stride,
+                                 long long conv_off, const int* __restrict__ seq_ids, const int* __restrict__ cu_q,
+                                 const int* __restrict__ slots, TO* out, int inner, int taps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int r = seq_ids[t];
+    const int i = t - cu_q[r];
+    const float* st = state + (size_t)slots[r] * slot_stride + conv_off;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < inner; c += gridDim.y * blockDim.x) {
+        float acc = b ? b[c] : 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int back = taps - 1 - j;                 // how many tokens before this one
+            const float v = back <= i ? xz[(size_t)(t - back) * ld + c]
+                                      : st[(size_t)c * (taps - 1) + (taps - 1 - (back - i))];
+            acc += w[(size_t)c * taps + j] * v;
+        }
+        out[(size_t)t * inner + c] = from_f<TO>(silu_f(acc));
+    }
+}
+
+RLLM_API int rllm_conv_silu(const float* xz, long long ld, const float* w, const float* b, const float* state,
+                            long long slot_stride, long long conv_off, const int* seq_ids, const int* cu_q,
+                            const int* slots, void* out, int out_dt, int n, int inner, int taps,
+                            cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (taps < 1 || inner <= 0) return (int)cudaErrorInvalidValue;
+    const dim3 grid(n, (inner + 255) / 256 > 64 ? 64 : (inner + 255) / 256);
+    if (out_dt == RLLM_F32)
+        return rllm_launch(conv_silu_kernel<float>, grid, dim3(256), 0, stream, xz, ld, w, b, state, slot_stride,
+                           conv_off, seq_ids, cu_q, slots, (float*)out, inner, taps);
+    return rllm_launch(conv_silu_kernel<bf16>, grid, dim3(256), 0, stream, xz, ld, w, b, state, slot_stride, conv_off,
+                       seq_ids, cu_q, slots, (bf16*)out, inner, taps);
+}
+
+// ------------------------------------------------------------------ selective scan
+// Per request r, channel c, state index n, over the request's tokens in order:
+//   dt = softplus(dtr[t, c] + dt_b[c]);  S[c, n] = exp(dt * A[c, n]) * S[c, n] + dt * x[t, c] * B[t, n]
+//   y  = sum_n S[c, n] * C[t, n] + D[c] * x[t, c];      out[t, c] = y * silu(z[t, c])
+// x: the convolution's output (activation type), B and C: columns of `low` (float32), z: columns
+// [inner, 2 inner) of xz.  SCAN_LANES lanes share a channel (state index n = lane + SCAN_LANES * k);
+// their partial sums are added in a fixed butterfly.  At the end the convolution's kept inputs
+// move on by this step's tokens.
+#define SCAN_LANES 4
+#define SCAN_CH 32            // channels per block (128 threads)
+#define SCAN_TOK 8            // tokens whose B and C are staged in shared memory at a time
+
+template <typename TA, int NPT>
+__global__ void __launch_bounds__(SCAN_LANES * SCAN_CH)
+selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float* low, long long ld_low, int b_off,
+                      int c_off, const float* dtr, const float* __restrict__ dt_b, const float* __restrict__ A,
+                      const float* __restrict__ Dp, float* state, long long slot_stride, long long conv_off,
+                      const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int inner, int N,
+                      int taps) {
+    extern __shared__ float bc[];                       // [SCAN_TOK][2][N]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.y;
+    const int t0 = cu_q[r], t1 = cu_q[r + 1];
+    const int lane = threadIdx.x % SCAN_LANES;
+    const int c_own = blockIdx.x * SCAN_CH + threadIdx.x / SCAN_LANES;
+    const bool live = c_own < inner;
+    const int c = live ? c_own : inner - 1;             // lanes beyond the last channel shadow it and write nothing
+    float* st = state + (size_t)slots[r] * slot_stride;
+    float S[NPT], a[NPT];
+#pragma unroll
+    for (int k = 0; k < NPT; ++k) {
+        const int n = lane + SCAN_LANES * k;
+        const bool on = n < N;
+        S[k] = on ? st[(size_t)c * N + n] : 0.f;
+        a[k] = on ? A[(size_t)c * N + n] : 0.f;
+    }
+    const float db = dt_b[c], dd = Dp[c];
+    for (int tb = t0; tb < t1; tb += SCAN_TOK) {
+        const int nt = min(SCAN_TOK, t1 - tb);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * 2 * N; i += blockDim.x) {
+            const int tt = i / (2 * N), j = i % (2 * N);
+            bc[i] = low[(size_t)(tb + tt) * ld_low + (j < N ? b_off + j : c_off + j - N)];
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const size_t t = tb + tt;
+            const float xv = to_f<TA>(x[t * inner + c]);
+            const float dt = softplus_f(dtr[t * inner + c] + db);
+            const float dx = dt * xv;
+            const float* Bt = bc + tt * 2 * N;
+            const float* Ct = Bt + N;
+            float part = 0.f;
+#pragma unroll
+            for (int k = 0; k < NPT; ++k) {
+                const int n = lane + SCAN_LANES * k;
+                if (n < N) {
+                    S[k] = expf(dt * a[k]) * S[k] + dx * Bt[n];
+                    part += S[k] * Ct[n];
+                }
+            }
+            part += __shfl_xor_sync(0xffffffffu, part, 1);
+            part += __shfl_xor_sync(0xffffffffu, part, 2);
+            if (lane == 0 && live) {
+                const float z = xz[t * ld_xz + inner + c];
+                out[t * inner + c] = from_f<TA>((part + dd * xv) * silu_f(z));
+            }
+        }
+    }
+    if (!live) return;
+#pragma unroll
+    for (int k = 0; k < NPT; ++k) {
+        const int n = lane + SCAN_LANES * k;
+        if (n < N) st[(size_t)c * N + n] = S[k];
+    }
+    if (lane == 0 && taps > 1) {
+        // kept inputs: the last taps-1 of (old kept inputs ++ this step's inputs), oldest first
+        float* cs = st + conv_off + (size_t)c * (taps - 1);
+        const int q = t1 - t0;
+        for (int k = 0; k < taps - 1; ++k) {
+            const int idx = q + k;                       // place in the joined sequence
+            cs[k] = idx < taps - 1 ? cs[idx] : xz[(size_t)(t0 + idx - (taps - 1)) * ld_xz + c];
+        }
+    }
+}
+
+RLLM_API int rllm_selective_scan(const void* x, int act_dt, const float* xz, long long ld_xz, const float* low,
+                                 long long ld_low, int b_off, int c_off, const float* dtr, const float* dt_b,
+                                 const float* A, const float* Dp, float* state, long long slot_stride,
+                                 long long conv_off, const int* cu_q, const int* slots, void* out, int n_requests,
+                                 int inner, int N, int taps, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (N <= 0 || N > SCAN_LANES * 64 || inner <= 0 || taps < 1) return (int)cudaErrorInvalidValue;
+    const dim3 grid((inner + SCAN_CH - 1) / SCAN_CH, n_requests), block(SCAN_LANES * SCAN_CH);
+    const size_t smem = (size_t)SCAN_TOK * 2 * N * sizeof(float);
+#define LAUNCH(TA, NPT)                                                                                          \
+    return rllm_launch(selective_scan_kernel<TA, NPT>, grid, block, smem, stream, (const TA*)x, xz, ld_xz, low,  \
+                       ld_low, b_off, c_off, dtr, dt_b, A, Dp, state, slot_stride, conv_off, cu_q, slots, (TA*)out, \
+                       inner, N, taps)
+#define BY_N(TA)                                                                                                 \
+    do {                                                                                                         \
+        if (N <= SCAN_LANES * 4) { LAUNCH(TA, 4); }                                                              \
+        if (N <= SCAN_LANES * 8) { LAUNCH(TA, 8); }                                                              \
+        if (N <= SCAN_LANES * 16) { LAUNCH(TA, 16); }                                                            \
+        if (N <= SCAN_LANES * 32) { LAUNCH(TA, 32); }                                                            \
+        LAUNCH(TA, 64);                                                                                          \
+    } while (0)
+    if (act_dt == RLLM_F32) BY_N(float);
+    BY_N(bf16);
+#undef BY_N
+#undef LAUNCH
+}
+
+// ------------------------------------------------------------------ token shift
+// out[s][t, c] = h[t, c] + (prev(t)[c] - h[t, c]) * mu[s][c] for s < n_streams; prev(t) is the row
+// before t of the same request, or the request's kept row (state) for the first token of its
+// portion -- zeros at the start of a sequence.  The kept row is advanced by the WKV kernel.
+template <typename TA>
+__global__ void token_shift_kernel(const TA* h, const float* __restrict__ mu, const float* state,
+                                   long long slot_stride, long long prev_off, const int* __restrict__ seq_ids,
+                                   const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int n, int d,
+                                   int n_streams) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int r = seq_ids[t];
+    const bool first = t == cu_q[r];
+    const float* pv = state + (size_t)slots[r] * slot_stride + prev_off;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        const float cur = to_f<TA>(h[(size_t)t * d + c]);
+        const float prev = first ? pv[c] : to_f<TA>(h[(size_t)(t - 1) * d + c]);
+        for (int s = 0; s < n_streams; ++s)
+            out[((size_t)s * n + t) * d + c] = from_f<TA>(cur + (prev - cur) * mu[(size_t)s * d + c]);
+    }
+}
+
+RLLM_API int rllm_token_shift(const void* h, int act_dt, const float* mu, const float* state, long long slot_stride,
+                              long long prev_off, const int* seq_ids, const int* cu_q, const int* slots, void* out,
+                              int n, int d, int n_streams, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (act_dt == RLLM_F32)
+        return rllm_launch(token_shift_kernel<float>, dim3(n), dim3(256), 0, stream, (const float*)h, mu, state,
+                           slot_stride, prev_off, seq_ids, cu_q, slots, (float*)out, n, d, n_streams);
+    return rllm_launch(token_shift_kernel<bf16>, dim3(n), dim3(256), 0, stream, (const bf16*)h, mu, state,
+                       slot_stride, prev_off, seq_ids, cu_q, slots, (bf16*)out, n, d, n_streams);
+}
+
+// ------------------------------------------------------------------ WKV with data-dependent decay
+// One block per (request, head); thread j owns column j of the head's state S [D keys][D values].
+// Per token, with r, k, v the head's rows of the projections, w = exp(-exp(wraw + w0)) the decay
+// per key channel and u the bonus of the current token:
+//   o[j] = sum_i r[i] * (S[i][j] + u[i] * k[i] * v[j]);     S[i][j] = w[i] * S[i][j] + k[i] * v[j]
+// then o is divided by its root mean square over the head (eps inside the root), multiplied by the
+// norm weight and by silu(gate), and stored in the activation type.  Tokens are taken WKV_TOK at a
+// time: r, k and w of the chunk go through shared memory, the outputs too, and the unit norms of
+// the chunk are worked out by the warps in turn.  The kept previous row moves on at the end.
+#define WKV_TOK 8
+
+template <typename TA, int DMAX>
+__global__ void __launch_bounds__(DMAX)
+wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw, const float* gp, long long ld,
+           const float* __restrict__ w0, const float* __restrict__ u, const float* __restrict__ norm_w, float eps,
+           float* state, long long slot_stride, long long prev_off, const TA* h, int width,
+           const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int H, int D) {
+    extern __shared__ float sm[];                        // r, k, w: [3][WKV_TOK][D]; o: [WKV_TOK][D]; u: [D]
+    float* s_r = sm;
+    float* s_k = s_r + WKV_TOK * D;
+    float* s_w = s_k + WKV_TOK * D;
+    float* s_o = s_w + WKV_TOK * D;
+    float* s_u = s_o + WKV_TOK * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) s_u[i] = u[(size_t)blockIdx.x * D + i];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.y, head = blockIdx.x, j = threadIdx.x;
+    const int t0 = cu_q[r], t1 = cu_q[r + 1];
+    float* st = state + (size_t)slots[r] * slot_stride;
+    float* Sg = st + (size_t)head * D * D;
+    const bool live = j < D;
+    float S[DMAX];
+#pragma unroll
+    for (int i = 0; i < DMAX; ++i) S[i] = (live && i < D) ? Sg[(size_t)i * D + j] : 0.f;
+    const size_t col = (size_t)head * D;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int tb = t0; tb < t1; tb += WKV_TOK) {
+        const int nt = min(WKV_TOK, t1 - tb);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * D; i += blockDim.x) {
+            const int tt = i / D, cc = i % D;
+            const size_t g = (size_t)(tb + tt) * ld + col + cc;
+            s_r[i] = rp[g];
+            s_k[i] = kp[g];
+            s_w[i] = expf(-expf(wraw[g] + w0[col + cc]));
+        }
+        __syncthreads();
+        if (live) {
+            for (int tt = 0; tt < nt; ++tt) {
+                const float vj = vp[(size_t)(tb + tt) * ld + col + j];
+                const float* rr = s_r + tt * D;
+                const float* kk = s_k + tt * D;
+                const float* ww = s_w + tt * D;
+                float o = 0.f;
+#pragma unroll
+                for (int i = 0; i < DMAX; ++i) {
+                    if (i < D) {
+                        const float kv = kk[i] * vj;
+                        o += rr[i] * (S[i] + s_u[i] * kv);
+                        S[i] = ww[i] * S[i] + kv;
+                    }
+                }
+                s_o[tt * D + j] = o;
+            }
+        }
+        __syncthreads();
+        for (int tt = warp; tt < nt; tt += n_warps) {
+            float ss = 0.f;
+            for (int i = lane; i < D; i += 32) ss += s_o[tt * D + i] * s_o[tt * D + i];
+            const float rs = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+            for (int i = lane; i < D; i += 32) {
+                const size_t g = (size_t)(tb + tt) * ld + col + i;
+                out[(size_t)(tb + tt) * H * D + col + i] =
+                    from_f<TA>(s_o[tt * D + i] * rs * norm_w[col + i] * silu_f(gp[g]));
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DMAX; ++i)
+            if (i < D) Sg[(size_t)i * D + j] = S[i];
+    }
+    if (head == 0 && t1 > t0) {
+        float* pv = st + prev_off;
+        for (int c = threadIdx.x; c < width; c += blockDim.x) pv[c] = to_f<TA>(h[(size_t)(t1 - 1) * width + c]);
+    }
+}
+
+RLLM_API int rllm_wkv(const float* rp, const float* kp, const float* vp, const float* wraw, const float* gp,
+                      long long ld, const float* w0, const float* u, const float* norm_w, float eps, float* state,
+                      long long slot_stride, long long prev_off, const void* h, int act_dt, int width,
+                      const int* cu_q, const int* slots, void* out, int n_requests, int H, int D,
+                      cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (D <= 0 || D > 256 || H <= 0) return (int)cudaErrorInvalidValue;
+    const dim3 grid(H, n_requests);
+    const size_t smem = (size_t)(4 * WKV_TOK + 1) * D * sizeof(float);
+#define LAUNCH(TA, DMAX)                                                                                       \
+    return rllm_launch(wkv_kernel<TA, DMAX>, grid, dim3(DMAX), smem, stream, rp, kp, vp, wraw, gp, ld, w0, u,  \
+                       norm_w, eps, state, slot_stride, prev_off, (const TA*)h, width, cu_q, slots, (TA*)out, H, D)
+#define BY_D(TA)                                                                                               \
+    do {                                                                                                       \
+        if (D <= 32) { LAUNCH(TA, 32); }                                                                       \
+        if (D <= 64) { LAUNCH(TA, 64); }                                                                       \
+        if (D <= 128) { LAUNCH(TA, 128); }                                                                     \
+        LAUNCH(TA, 256);                                                                                       \
+    } while (0)
+    if (act_dt == RLLM_F32) BY_D(float);
+    BY_D(bf16);
+#undef BY_D
+#undef LAUNCH
+}
+
+RLLM_PACKED(rllm_conv_silu)
+RLLM_PACKED(rllm_selective_scan)
+RLLM_PACKED(rllm_token_shift)
+RLLM_PACKED(rllm_wkv)

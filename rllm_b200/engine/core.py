@@ -278,19 +278,23 @@ class Engine:
             q_lens=meta["q_lens"], start_pos=meta["start_pos"], ctx_lens_host=meta["ctx_lens"],
             max_q_len=max(meta["q_lens"]), max_ctx_len=max(meta["ctx_lens"]))
         dev_slots, dev_tables = dev[7:7 + G], dev[7 + G:7 + 2 * G]
+        def view(i, place):
+            if place is None:
+                return None
+            if place[0] == "kv":
+                _, g, plane = place
+                k, v = cache.paged[g].planes(plane)
+                return PagedKVView(k, v, dev_tables[g], dev_slots[g], self.block_size,
+                                   write=cache.cache_of[i] is None, group=g)
+            _, g, plane = place
+            return StateView(cache.stateful[g].state[plane], ctx.state_slots, write=cache.cache_of[i] is None)
+
         views = []
         for i, place in enumerate(cache.entry_place):
-            if place is None:
-                views.append(None)
-            elif place[0] == "kv":
-                _, g, plane = place
-                pool = cache.paged[g].pool
-                views.append(PagedKVView(pool[plane, 0], pool[plane, 1], dev_tables[g], dev_slots[g],
-                                         self.block_size, write=cache.cache_of[i] is None, group=g))
+            if isinstance(place, tuple) and (not place or not isinstance(place[0], str)):
+                views.append(tuple(view(i, p) for p in place))          # one view per need of the mixer
             else:
-                _, g, plane = place
-                views.append(StateView(cache.stateful[g].state[plane], ctx.state_slots,
-                                       write=cache.cache_of[i] is None))
+                views.append(view(i, place))
         return ctx, views
 
     # ------------------------------------------------------------------ the step

@@ -76,10 +76,14 @@ class DecoderModel:
         self.blocks = [part_class("block", ls.block)(ls, runtime) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.lm_head = build_part("lm_head", spec.lm_head, runtime)
+        self.junctions = [build_part("junction", js, runtime) for js in getattr(spec, "junctions", ())]
+        self.residual_scale = float(getattr(spec, "residual_scale", 1.0))
         self.run_order = list(spec.run_order)
         for i, e in enumerate(self.run_order):
             if not 0 <= e.layer < len(self.blocks):
                 raise ValueError(f"run entry {i} names layer {e.layer}, but there are {len(self.blocks)}")
+            if e.junction is not None and not 0 <= e.junction < len(self.junctions):
+                raise ValueError(f"run entry {i} names junction {e.junction}, but there are {len(self.junctions)}")
         self.loaded = False
         # decode steps of this model may be captured into CUDA graphs: every part says it can be
         self.capture_safe = all(getattr(p, "CAPTURE_SAFE", False) for p in self._weighted_parts() + self.blocks)
@@ -102,6 +106,7 @@ class DecoderModel:
         ps = [self.embedding]
         for b in self.blocks:
             ps.extend(b.parts())
+        ps += self.junctions
         ps += [self.final_norm, self.lm_head]
         return ps
 
@@ -125,7 +130,7 @@ class DecoderModel:
             if p is self.lm_head:
                 continue
             p.load(tensors)
-        shared[self.embedding.prefix + "weight"] = self.embedding.weight
+        shared[getattr(self.embedding, "name", self.embedding.prefix + "weight")] = self.embedding.weight
         self.lm_head.load(tensors, shared=shared)
         self.loaded = True
 
@@ -145,12 +150,18 @@ class DecoderModel:
         (None when no row is wanted).  `views[i]` is run entry i's cache view."""
         ctx.scratch = {}                 # what the layers of this pass share (a captured pass makes its own again)
         x = self.embedding.forward(ctx.tokens)
+        x0 = x.clone() if self.junctions else None       # the embedding output, for the junctions
         pending = None
         from ..csrc import ops
         traces = {} if (TRACE_LAYERS and x.is_cuda and ops.can_trace()) else None
         for i, e in enumerate(self.run_order):
             block = self.blocks[e.layer]
+            if e.junction is not None:
+                x = self.junctions[e.junction].forward(x, x0, pending, self.residual_scale, e.junction_arg)
+                pending = None
             nxt = self.blocks[self.run_order[i + 1].layer] if i + 1 < len(self.run_order) else None
+            if nxt is not None and self.run_order[i + 1].junction is not None:
+                nxt = None                               # a junction follows: the block prepares nothing beyond itself
             defers = getattr(block, "DEFERS_NORM", False) and getattr(nxt, "DEFERS_NORM", False)
             key = None
             if traces is not None and self._builds[e.layer] is not None:
@@ -176,7 +187,11 @@ class DecoderModel:
                 pending = block.forward(x, pending, ctx, views[i])
         if ctx.logit_rows is None or ctx.logit_rows.numel() == 0:
             return None
-        h = self.final_norm.forward(x, pending, rows=ctx.logit_rows, write_x=False)
+        if self.residual_scale != 1.0:
+            h = self.final_norm.forward(x, pending, rows=ctx.logit_rows, write_x=False,
+                                        delta_scale=self.residual_scale)
+        else:
+            h = self.final_norm.forward(x, pending, rows=ctx.logit_rows, write_x=False)
         return self.lm_head.forward(h)
 
 

@@ -14,7 +14,7 @@ from typing import Any, Callable, Mapping, Optional
 
 import torch
 
-CATEGORIES = ("embedding", "norm", "position", "mixer", "ffn", "block", "lm_head")
+CATEGORIES = ("embedding", "norm", "position", "mixer", "ffn", "block", "lm_head", "junction")
 _REGISTRY: dict[str, dict[str, Callable]] = {c: {} for c in CATEGORIES}
 
 
@@ -63,10 +63,18 @@ class Runtime:
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values in pages.  `window` > 0: only the last `window` keys are ever read, so
-    pages that the window has passed can be given back."""
+    pages that the window has passed can be given back; with `keep_first` > 0 the first that many
+    keys of a request stay readable all the same, and their pages are kept.  `v_head_dim`: size of
+    a value head where it differs from a key head (0: the same)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    keep_first: int = 0
+    v_head_dim: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -111,7 +119,8 @@ class Part:
 class Mixer(Part):
     """Token mixer interface.
 
-    ``cache_need()`` returns a PagedKVNeed, a StateNeed or None.
+    ``cache_need()`` returns a PagedKVNeed, a StateNeed, None, or a tuple of needs (a mixer that is
+    several mixers side by side); `cache` is then a tuple of views in the same order.
     ``forward(h, ctx, cache, position)``: `h` [n, hidden] normed activations in the runtime's
     dtype, `ctx` the step's :class:`~rllm_b200.engine.batch.StepContext`, `cache` the view of
     this run entry's cache (:class:`~rllm_b200.cache.views.PagedKVView` or ``StateView``; None
@@ -136,9 +145,19 @@ class FeedForward(Part):
 
 
 class Norm(Part):
-    """``forward(x, delta=None, rows=None, write_x=True)``: adds `delta` to the float32 residual
-    stream `x` (in place when write_x), optionally gathers `rows`, returns the normed rows in the
-    runtime's dtype."""
+    """``forward(x, delta=None, rows=None, write_x=True, delta_scale=1.0)``: adds `delta_scale *
+    delta` to the float32 residual stream `x` (in place when write_x), optionally gathers `rows`,
+    returns the normed rows in the runtime's dtype."""
 
-    def forward(self, x, delta=None, rows=None, write_x=True):
+    def forward(self, x, delta=None, rows=None, write_x=True, delta_scale=1.0):
+        raise NotImplementedError
+
+
+class Junction(Part):
+    """A part that stands between two run entries and rewrites the whole residual stream:
+    ``forward(x, x0, delta, delta_scale, arg) -> new x`` with `x` the float32 stream, `delta` what
+    the block before still owes it (or None), `x0` the embedding output of the step's tokens and
+    `arg` the run entry's `junction_arg`."""
+
+    def forward(self, x, x0, delta, delta_scale, arg):
         raise NotImplementedError

@@ -8,6 +8,13 @@ return its output, which the next norm then adds in the same kernel that normali
 (AxiomOperator/rllm fuses the next layer's norm into the residual add:
 crates/rllm-model/src/qwen3.rs:192-208).
 
+With the block parameter ``residual_mult`` = m (a constant of the model, the same for all its
+layers) a sublayer's output joins the stream multiplied by m: x += m * mixer(norm(x)), x += m *
+ffn(norm(x)); the multiplication happens inside the norm kernel that adds the output (and in the
+model's final norm, or a junction, for the last one).  A layer whose spec has no feed-forward
+has the mixer sublayer only.  Such blocks take the plain path below (no deferred norms, no
+accumulation into the stream by the products).
+
 A block's interface: ``__init__(layer_spec, runtime)`` builds its parts from the registries;
 ``parts()`` lists them; ``forward(x, pending, ctx, cache) -> pending``.
 
@@ -42,15 +49,24 @@ def deferral(before, norm, after, m: int):
 @register_part("block", "pre_norm")
 class PreNormBlock:
     def __init__(self, layer_spec, runtime):
+        self.residual_mult = float(dict(getattr(layer_spec, "block_params", None) or {}).get("residual_mult", 1.0))
         self.norm_mixer = build_part("norm", layer_spec.norms["mixer"], runtime)
-        self.norm_ffn = build_part("norm", layer_spec.norms["ffn"], runtime)
         self.mixer = build_part("mixer", layer_spec.mixer, runtime)
-        self.ffn = build_part("ffn", layer_spec.ffn, runtime)
+        self.ffn = build_part("ffn", layer_spec.ffn, runtime) if layer_spec.ffn is not None else None
+        self.norm_ffn = build_part("norm", layer_spec.norms["ffn"], runtime) if self.ffn is not None else None
         self.position = (build_part("position", layer_spec.position, runtime)
                          if layer_spec.position is not None else None)
+        # the fused arrangements (products that add into the stream, norms without a kernel, recorded
+        # layers) are those of the unscaled two-sublayer block
+        self.scaled = self.residual_mult != 1.0 or self.ffn is None
+        if self.scaled:
+            self.DEFERS_NORM = self.TRACEABLE = False
+        self.CAPTURE_SAFE = all(getattr(p, "CAPTURE_SAFE", False) for p in self.parts())
 
     def parts(self):
-        ps = [self.norm_mixer, self.mixer, self.norm_ffn, self.ffn]
+        ps = [self.norm_mixer, self.mixer]
+        if self.ffn is not None:
+            ps += [self.norm_ffn, self.ffn]
         if self.position is not None:
             ps.append(self.position)
         return ps
@@ -62,7 +78,18 @@ class PreNormBlock:
     def entry(self):
         return self.norm_mixer, self.mixer
 
+    def _forward_scaled(self, x, pending, ctx, cache):
+        s = self.residual_mult
+        h = self.norm_mixer.forward(x, pending, delta_scale=s)
+        a = self.mixer.forward(h, ctx, cache, self.position)
+        if self.ffn is None:
+            return a
+        h = self.norm_ffn.forward(x, a, delta_scale=s)
+        return self.ffn.forward(h, ctx)
+
     def forward(self, x, pending, ctx, cache, next_entry=None):
+        if self.scaled:
+            return self._forward_scaled(x, pending, ctx, cache)
         m = x.shape[0]
         h = pending if isinstance(pending, ops.NormedRows) else self.norm_mixer.forward(x, pending)
         later = deferral(self.mixer, self.norm_ffn, self.ffn, m)

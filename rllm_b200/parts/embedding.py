@@ -21,13 +21,14 @@ class Embedding(Part):
         super().__init__(params, prefix, runtime)
         self.vocab_size = int(params["vocab_size"])
         self.hidden_size = int(params["hidden_size"])
+        self.name = params.get("tensor") or self.prefix + "weight"      # the table's name in the weight file
         self.weight = None
 
     def expected_tensors(self):
-        return {self.prefix + "weight": ((self.vocab_size, self.hidden_size), "matrix")}
+        return {self.name: ((self.vocab_size, self.hidden_size), "matrix")}
 
     def load(self, tensors):
-        self.weight = self._to_device(tensors[self.prefix + "weight"])
+        self.weight = self._to_device(tensors[self.name])
 
     def forward(self, tokens):
         out = torch.empty((tokens.numel(), self.hidden_size), dtype=torch.float32, device=tokens.device)
@@ -43,22 +44,23 @@ class LMHead(Part):
         self.vocab_size = int(params["vocab_size"])
         self.hidden_size = int(params["hidden_size"])
         self.tied_to = params.get("tied_to")
+        self.name = params.get("tensor") or self.prefix + "weight"
         self.weight = None
 
     def expected_tensors(self):
         if self.tied_to:
             return {}
-        return {self.prefix + "weight": ((self.vocab_size, self.hidden_size), "matrix")}
+        return {self.name: ((self.vocab_size, self.hidden_size), "matrix")}
 
     def ignorable_tensors(self):
         """A tied model may still store the head; it is not read."""
-        return {self.prefix + "weight"} if self.tied_to else set()
+        return {self.name} if self.tied_to else set()
 
     def load(self, tensors, shared=None):
         if self.tied_to:
             self.weight = shared[self.tied_to]
         else:
-            self.weight = self._to_device(tensors[self.prefix + "weight"])
+            self.weight = self._to_device(tensors[self.name])
 
     def forward(self, h):
         """h [m, hidden] normed rows -> float32 logits [m, vocab]."""

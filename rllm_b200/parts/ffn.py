@@ -1,4 +1,8 @@
-"""SwiGLU feed-forward: out = (silu(h . Wg^T) * (h . Wu^T)) . Wd^T, no biases
+"""Feed-forwards.  ``dense_act``: out = act(h . Wup^T) . Wdown^T with one of the activations of
+csrc/rowwise.cu (relu2: the square of relu), no gate, no biases; parameters hidden_size,
+intermediate_size, activation; tensors <prefix>up, <prefix>down.
+
+SwiGLU feed-forward: out = (silu(h . Wg^T) * (h . Wu^T)) . Wd^T, no biases
 (AxiomOperator/rllm: crates/rllm-core/src/lib.rs:247-262, crates/rllm-cpu/src/lib.rs:292-298).
 Parameters: hidden_size, intermediate_size.  Tensors: <prefix>{gate,up,down}_proj.weight.
 Load-time transform: gate and up are stacked into one [2F, hidden] matrix so that one product
@@ -56,3 +60,31 @@ class SwiGLU(FeedForward):
             ops.linear(act, self.w_down, out=residual, accumulate=True, follow=before)
             return None
         return ops.linear(act, self.w_down, out_dtype=torch.float32, follow=before)
+
+
+@register_part("ffn", "dense_act")
+class DenseAct(FeedForward):
+    CAPTURE_SAFE = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.hidden_size = int(params["hidden_size"])
+        self.intermediate_size = int(params["intermediate_size"])
+        self.activation = params["activation"]
+        if self.activation not in ops.ACT:
+            raise ValueError(f"dense_act: unknown activation {self.activation!r}")
+        self.w_up = self.w_down = None
+
+    def expected_tensors(self):
+        F, d = self.intermediate_size, self.hidden_size
+        return {self.prefix + "up": ((F, d), "matrix"), self.prefix + "down": ((d, F), "matrix")}
+
+    def load(self, tensors):
+        self.w_up = self._to_device(tensors[self.prefix + "up"])
+        self.w_down = self._to_device(tensors[self.prefix + "down"])
+
+    def forward(self, h, ctx=None, residual=None):
+        up = ops.linear(h, self.w_up, out_dtype=torch.float32)
+        act = torch.empty(up.shape, dtype=self.runtime.dtype, device=h.device)
+        ops.rows_act(up, act, act=self.activation)
+        return ops.linear(act, self.w_down, out_dtype=torch.float32)

@@ -4,7 +4,8 @@ out = v * (1 / sqrt(mean(v^2) + eps)) * weight, v = x (+ delta); the weight mult
 directly (no 1 + w), statistics in float32 (AxiomOperator/rllm:
 crates/rllm-cpu/src/lib.rs:241-254; the fusion with the residual add is
 crates/rllm-cuda/kernels/kernels.cu:794-820 and crates/rllm-model/src/qwen3.rs:202-208).
-Parameters: size, eps.  Tensor: <prefix>weight [size], kept in float32.
+Parameters: size, eps, optionally `tensor` (the weight's full name).  Tensor: <prefix>weight
+[size], kept in float32.  `delta_scale`: the delta joins the stream multiplied by it.
 """
 from __future__ import annotations
 
@@ -23,20 +24,22 @@ class RMSNorm(Norm):
         super().__init__(params, prefix, runtime)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.name = params.get("tensor") or self.prefix + "weight"
         self.weight = None
 
     def expected_tensors(self):
-        return {self.prefix + "weight": ((self.size,), "norm")}
+        return {self.name: ((self.size,), "norm")}
 
     def load(self, tensors):
-        self.weight = self._to_device(tensors[self.prefix + "weight"], torch.float32)
+        self.weight = self._to_device(tensors[self.name], torch.float32)
 
     def deferrable(self):
         """(weight, eps) for a product kernel that prepares this norm in its epilogue (the division by
         the rms then happens in the product after it: csrc/ops.NormedRows)."""
         return self.weight, self.eps
 
-    def forward(self, x, delta=None, rows=None, write_x=True):
+    def forward(self, x, delta=None, rows=None, write_x=True, delta_scale=1.0):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=self.runtime.dtype, device=x.device)
-        return ops.add_rms_norm(x, delta, self.weight, out, self.eps, rows=rows, write_x=write_x)
+        return ops.add_rms_norm(x, delta, self.weight, out, self.eps, rows=rows, write_x=write_x,
+                                delta_scale=delta_scale)

@@ -23,7 +23,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--block-size", type=int, default=PAGE_TOKENS)
-    ap.add_argument("--max-requests", type=int, default=16)
+    ap.add_argument("--max-requests", type=int, default=4,
+                    help="requests that are live at a time: the cache has this many state slots (default 4)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 

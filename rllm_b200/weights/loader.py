@@ -87,6 +87,13 @@ def weight_files(model_dir) -> tuple[dict, list]:
     return where, files
 
 
+def shape_fits(shape, expected) -> bool:
+    """Whether a stored shape is the expected one; None in `expected` stands for a size that only
+    the file gives (a part then takes it from the tensor when it loads)."""
+    shape, expected = tuple(shape), tuple(expected)
+    return len(shape) == len(expected) and all(e is None or int(e) == int(s) for s, e in zip(shape, expected))
+
+
 def load_checked(model_dir, expected: Mapping[str, tuple], ignorable: Iterable[str] = ()) -> dict:
     """Reads the folder's weights: ``model.safetensors``, or every shard that
     ``model.safetensors.index.json`` names.  `expected` maps tensor name -> shape; names in
@@ -115,8 +122,8 @@ def load_checked(model_dir, expected: Mapping[str, tuple], ignorable: Iterable[s
         shown = model_dir / (INDEX_NAME if where else SINGLE_NAME)
         missing = sorted(n for n in expected if n not in home)
         unexpected = sorted(n for n in home if n not in expected and n not in ignorable)
-        wrong = sorted((n, opened[home[n]].shape(n), tuple(expected[n])) for n in expected
-                       if n in home and opened[home[n]].shape(n) != tuple(expected[n]))
+        wrong = sorted(((n, opened[home[n]].shape(n), tuple(expected[n])) for n in expected
+                        if n in home and not shape_fits(opened[home[n]].shape(n), expected[n])), key=str)
         if missing or unexpected or wrong:
             raise WeightMismatchError(shown, missing, unexpected, wrong)
         return {n: normalize_dtype(opened[home[n]].tensor(n)) for n in expected}

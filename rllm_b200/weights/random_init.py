@@ -25,12 +25,23 @@ def _generator(seed: int, name: str, device="cpu") -> torch.Generator:
 
 def random_tensors(expected: dict, seed: int, dtype=torch.bfloat16, std=0.02, norm_std=0.1,
                    device="cpu") -> dict:
-    """`expected`: name -> (shape, role) with role 'norm' (1 + noise) or anything else (noise)."""
+    """`expected`: name -> (shape, role) with role 'norm' (1 + noise), 'mix' (inside (0, 1)), 'conv'
+    (noise / sqrt(taps)) or anything else (noise)."""
     out = {}
     for name, (shape, role) in expected.items():
+        if any(s is None for s in shape):
+            raise ValueError(f"tensor {name!r}: the configuration leaves a size open that only a weight file "
+                             f"gives; random weights need it set ({shape})")
         g = _generator(seed, name, device)
         t = torch.randn(shape, generator=g, dtype=torch.float32, device=device)
-        t = 1.0 + norm_std * t if role == "norm" else std * t
+        if role == "norm":
+            t = 1.0 + norm_std * t
+        elif role == "mix":                  # interpolation weights between two rows: inside (0, 1)
+            t = torch.sigmoid(t)
+        elif role == "conv":                 # a few taps per channel: of the order of 1 / taps
+            t = t / max(1, shape[-1]) ** 0.5
+        else:
+            t = std * t
         out[name] = t.to(dtype)
     return out
 
