@@ -103,6 +103,96 @@ def weight_bytes(model):
     return total
 
 
+def falalix_shape(width: int) -> dict:
+    """A Falalix configuration with layer sizes of a real model of that width: the cycle Mamba
+    (no feed-forward), parallel, parallel, Mamba, parallel, parallel, the layers 1..3 run twice."""
+    mamba = {"type": "mamba1", "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}, "mlp": None}
+    heads = max(8, width // 128)
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                              "mask": {"size": 1024, "keep_first": 4}, "scale": 128 ** -0.5},
+                     "right": {"heads": width // 64, "dim": 64, "decay_rank": 64},
+                     "left_scale": 0.6, "right_scale": 0.9},
+           "mlp": {"kind": "dense", "ff": 3 * width}}
+    return {"architecture": "Falalix", "vocab": 32768, "width": width, "layers": [mamba, par, par, mamba, par, par],
+            "loop": {"start": 1, "stop": 4, "times": 2}, "norm": {"eps": 1e-6}, "residual_mult": 0.3}
+
+
+def qwen3_shape(width: int, layers: int) -> dict:
+    heads = max(8, width // 128)
+    return dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=3 * width, vocab_size=32768)
+
+
+def falalix_compare(a):
+    """Prefill (one step of 2,048 tokens) and decode (batch 8 behind 2,048-token prompts, replayed
+    from CUDA graphs) of Falalix-shaped models beside Qwen3-shaped models of the same width, number
+    of layer runs and feed-forward width; random bf16 weights; CUDA events, synchronize on both
+    sides.  With RLLM_B200_PROFILE=1 the launchers' device times are printed at exit instead."""
+    import torch
+    from rllm_b200.config import config_from_dict
+    from rllm_b200.csrc import ops
+    from rllm_b200.engine import Engine, StepItem
+    from rllm_b200.models.model import random_model
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(1)
+    widths = {"1k": 1024, "2k": 2048, "4k": 4096}
+    out = {"metric": "Falalix-shaped against Qwen3-shaped models of equal width and depth: prefill tok/s "
+                     "(2,048 tokens, one step) and decode tok/s (batch 8, 2,048-token prompts)",
+           "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "dtype": "bf16", "impl": "ours",
+           "data": "synthetic: random weights, uniform random token ids", "sizes": {}}
+    launches0 = ops.launch_count()
+    clocks = ClockSampler()
+    clocks.start()
+    for size in a.sizes.split(","):
+        width = widths[size]
+        row = {}
+        for name in ("falalix", "qwen3"):
+            fal = falalix_shape(width)
+            runs = len(fal["layers"]) + (fal["loop"]["stop"] - fal["loop"]["start"]) * (fal["loop"]["times"] - 1)
+            config = config_from_dict(fal if name == "falalix" else qwen3_shape(width, runs))
+            model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0", generate_on_device=True)
+            V = model.spec.vocab_size
+            eng = Engine(model, block_size=32, max_tokens=a.batch * (PROMPT + 256), max_requests=a.batch)
+            prompts = [torch.randint(0, V, (PROMPT,), generator=g).tolist() for _ in range(a.batch)]
+            times = []
+            for rep in range(4):                       # prefill of one prompt in one step; the first loads kernels
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                s.record()
+                eng.step([StepItem("p", prompts[0], [PROMPT - 1])])
+                e.record()
+                torch.cuda.synchronize()
+                eng.finish("p")
+                if rep:
+                    times.append(s.elapsed_time(e))
+            for b in range(a.batch):
+                eng.step([StepItem(b, prompts[b], [])])
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for i in range(a.steps + a.warmup):
+                if i == a.warmup:
+                    torch.cuda.synchronize()
+                    s.record()
+                eng.step([StepItem(b, [(7 * i + b) % V], [0]) for b in range(a.batch)])
+            e.record()
+            torch.cuda.synchronize()
+            ops.check_device_errors("cuda:0")
+            ms = s.elapsed_time(e) / a.steps
+            row[name] = {"layer_runs": runs, "weights_gb": round(weight_bytes(model) / 1e9, 3),
+                         "prefill_tok_s": round(PROMPT * 1000.0 / min(times), 1), "prefill_ms": round(min(times), 3),
+                         "decode_tok_s": round(a.batch * 1000.0 / ms, 1), "decode_ms": round(ms, 4)}
+            del eng, model
+            gc.collect()
+            torch.cuda.empty_cache()
+        out["sizes"][size] = row
+    out["clocks"] = clocks.stop()
+    out["gpu_launches"] = ops.launch_count() - launches0
+    out["config"] = {"batch": a.batch, "prompt_len": PROMPT, "kv_block": 32,
+                     "l2": "no flush: a step streams the model's weights and activations of 2,048 tokens"}
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     global PROMPT, CTX
     ap = argparse.ArgumentParser()
@@ -117,9 +207,12 @@ def main():
     ap.add_argument("--ctx", type=int, default=None, help="tokens a request may hold (default: twice the prompt)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "falalix"],
                     help="decode: the default line.  serving: --requests prompts of 16..2,048 tokens with 128..512 "
-                         "generated tokens each through LLM.generate (continuous batching), one line of its own")
+                         "generated tokens each through LLM.generate (continuous batching), one line of its own.  "
+                         "falalix: prefill and decode of Falalix-shaped models (--sizes) beside Qwen3-shaped models of "
+                         "equal width, depth and feed-forward, one line of its own")
+    ap.add_argument("--sizes", default="1k,2k,4k", help="falalix: model widths to run (1k, 2k, 4k)")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--parallel", type=int, default=32, help="serving: requests running at once")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="serving: prompt tokens per step")
@@ -133,6 +226,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.workload == "falalix":
+        return falalix_compare(a)
     PROMPT = a.prompt_len
     CTX = a.ctx if a.ctx is not None else 2 * PROMPT
 

@@ -41,6 +41,7 @@ struct FlashParams {
     int n_pages;              // pages of the pool: a table entry outside [0, n_pages) is refused (page 0 is read, *err set)
     int* err;                 // the error word, or null
     int H, K, bs, window;
+    int keep_first;           // with a window: the first keys of a request stay visible behind it (0: none)
     int TT, GH, head_chunks;  // tokens per tile, heads per token in a tile, chunks of the GQA group
     int split_keys;           // 0: no split
     int part_rows;            // rows kept per partial (TT * GH)
@@ -109,8 +110,17 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     const int pos_first = p.positions[tok0], pos_last = p.positions[tok0 + nt - 1];
     int lo = p.window > 0 ? max(0, pos_first + 1 - p.window) : 0;
     lo = lo / BN * BN;
+    // The kept first keys that lie before the first window tile: [0, sink_end).  Without splits they are
+    // extra tiles ahead of the window's; with splits the last split is theirs (and may be empty).  Kept
+    // keys inside the window tiles are let through by the mask there.
+    const int keepv = p.window > 0 ? p.keep_first : 0;
+    const int sink_end = min(keepv, lo);
+    const bool sink_split = p.split_keys > 0 && keepv > 0 && blockIdx.z == gridDim.z - 1;
     int kb = lo, ke = pos_last + 1;
-    if (p.split_keys > 0) {
+    if (sink_split) {
+        kb = 0;
+        ke = sink_end;
+    } else if (p.split_keys > 0) {
         kb = lo + blockIdx.z * p.split_keys;
         ke = min(ke, kb + p.split_keys);
     }
@@ -121,8 +131,8 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     const int tl0 = R0 / p.GH, hl0 = R0 % p.GH, tl1 = R1 / p.GH, hl1 = R1 % p.GH;
     const bool valid0 = tl0 < nt && hl0 < nh, valid1 = tl1 < nt && hl1 < nh;
     const int pos0 = valid0 ? p.positions[tok0 + tl0] : -1, pos1 = valid1 ? p.positions[tok0 + tl1] : -1;
-    const int first0 = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;
-    const int first1 = p.window > 0 ? max(0, pos1 + 1 - p.window) : 0;
+    const int first0 = (p.window > 0 && !sink_split) ? max(0, pos0 + 1 - p.window) : 0;
+    const int first1 = (p.window > 0 && !sink_split) ? max(0, pos1 + 1 - p.window) : 0;
     const int hi0 = min(pos0 + 1, ke), hi1 = min(pos1 + 1, ke);
 
     if (kb >= ke) {                                // an empty split: mark it so
@@ -153,8 +163,8 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     static_assert((NW * 32) % CH == 0, "threads must cover whole rows of chunks");
     constexpr int ROWS_PER_PASS = NW * 32 / CH;
     const int my_chunk = tid % CH, my_row0 = tid / CH;
-    const int last_blk = (ke - 1) / p.bs;
-    auto load_tile = [&](int stage, int kt) {
+    auto load_tile = [&](int stage, int kt, int kend) {
+        const int last_blk = (kend - 1) / p.bs;
         unsigned char* sk = smem + (size_t)stage * 2 * TILE_BYTES;
         unsigned char* sv = sk + TILE_BYTES;
         // page by page: one table look-up and one base address per page, then a stride per row
@@ -172,7 +182,7 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
 #pragma unroll 4
             for (; r < rows_here; r += ROWS_PER_PASS) {
                 const int row = row0 + r;
-                const bool ok = blk <= last_blk && kt + row < ke;
+                const bool ok = blk <= last_blk && kt + row < kend;
                 const uint32_t dst = row * (HD * 2) + ((my_chunk ^ (row & 7)) << 4);
                 cp_async16(smem_u32(sk + dst), ksrc + (ok ? r * HD : 0), ok ? 16 : 0);
                 cp_async16(smem_u32(sv + dst), vsrc + (ok ? r * HD : 0), ok ? 16 : 0);
@@ -186,13 +196,17 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     for (int j = 0; j < NT_O; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    const int n_tiles = (ke - kb + BN - 1) / BN;
-    load_tile(0, kb);
+    const int n_sink = (p.split_keys == 0 && sink_end > 0) ? (sink_end + BN - 1) / BN : 0;   // tiles of kept keys first
+    const int n_tiles = n_sink + (ke - kb + BN - 1) / BN;
+    auto tile_start = [&](int i) { return i < n_sink ? i * BN : kb + (i - n_sink) * BN; };
+    auto tile_end = [&](int i) { return i < n_sink ? sink_end : ke; };
+    load_tile(0, tile_start(0), tile_end(0));
     cp_async_commit();
     const int mi = lane >> 3, ri = lane & 7;
     for (int it = 0; it < n_tiles; ++it) {
-        const int kt = kb + it * BN;
-        if (it + 1 < n_tiles) load_tile((it + 1) & 1, kt + BN);
+        const int kt = tile_start(it);
+        const bool in_sink = it < n_sink;
+        if (it + 1 < n_tiles) load_tile((it + 1) & 1, tile_start(it + 1), tile_end(it + 1));
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
@@ -216,7 +230,9 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
             }
         }
         // ---- scale, mask, online softmax
-        const bool need_mask = (kt + BN > min(hi0, hi1)) || (kt < max(first0, first1));
+        const int f0 = in_sink ? 0 : first0, f1 = in_sink ? 0 : first1;
+        const int h0 = in_sink ? min(hi0, sink_end) : hi0, h1 = in_sink ? min(hi1, sink_end) : hi1;
+        const bool need_mask = in_sink || (kt + BN > min(hi0, hi1)) || (kt < max(first0, first1));
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int j = 0; j < NT_S; ++j) {
@@ -225,7 +241,8 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
                 float v = s[j][e] * p.scale_log2;
                 if (need_mask) {
                     const int key = kt + 8 * j + 2 * t + (e & 1);
-                    const bool vis = (e < 2) ? (key >= first0 && key < hi0) : (key >= first1 && key < hi1);
+                    const bool vis = (e < 2) ? ((key >= f0 || key < keepv) && key < h0)
+                                             : ((key >= f1 || key < keepv) && key < h1);
                     if (!vis) v = -INFINITY;
                 }
                 s[j][e] = v;
@@ -349,8 +366,17 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
     const int pos_first = p.positions[tok0], pos_last = p.positions[tok0 + nt - 1];
     int lo = p.window > 0 ? max(0, pos_first + 1 - p.window) : 0;
     lo = lo / BN * BN;
+    // The kept first keys that lie before the first window tile: [0, sink_end).  Without splits they are
+    // extra tiles ahead of the window's; with splits the last split is theirs (and may be empty).  Kept
+    // keys inside the window tiles are let through by the mask there.
+    const int keepv = p.window > 0 ? p.keep_first : 0;
+    const int sink_end = min(keepv, lo);
+    const bool sink_split = p.split_keys > 0 && keepv > 0 && blockIdx.z == gridDim.z - 1;
     int kb = lo, ke = pos_last + 1;
-    if (p.split_keys > 0) {
+    if (sink_split) {
+        kb = 0;
+        ke = sink_end;
+    } else if (p.split_keys > 0) {
         kb = lo + blockIdx.z * p.split_keys;
         ke = min(ke, kb + p.split_keys);
     }
@@ -366,7 +392,7 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
         hlc[x] = rowc[x] % p.GH;
         validc[x] = tlc[x] < nt && hlc[x] < nh;
         const int pos = validc[x] ? p.positions[tok0 + tlc[x]] : -1;
-        firstc[x] = p.window > 0 ? max(0, pos + 1 - p.window) : 0;
+        firstc[x] = (p.window > 0 && !sink_split) ? max(0, pos + 1 - p.window) : 0;
         hic[x] = min(pos + 1, ke);
     }
     if (kb >= ke) {                                // an empty split: mark it so
@@ -520,7 +546,7 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
                 if (need_mask) {
                     const int key = kt + 16 * j + g + (e >> 1) * 8;
                     const int x = e & 1;
-                    if (!(key >= firstc[x] && key < hic[x])) v = -INFINITY;
+                    if (!((key >= firstc[x] || key < keepv) && key < hic[x])) v = -INFINITY;
                 }
                 s[j][e] = v;
             }
@@ -698,14 +724,17 @@ static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_split
 // part_ml the same with 2 in place of hd).  TT * GH must not exceed the tile's rows; split_keys must be
 // a multiple of 32.  Returns cudaErrorInvalidValue for a
 // head size other than 64 or 128.
-RLLM_API int rllm_paged_flash_attention(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                        float* part_o, float* part_ml, const int* positions, const int* cu_q,
-                                        const int* block_table, int table_stride, const int* tile_req,
-                                        const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
-                                        float scale, int window, int mode, int TT, int GH, int head_chunks,
-                                        int split_keys, int n_splits, long long n_pages, int* err,
-                                        cudaStream_t stream) {
+// keep_first > 0 (with a window): the first keys of a request stay visible behind the window; in mode 1
+// the LAST of the n_splits splits then belongs to them, so the caller counts one split more.
+RLLM_API int rllm_paged_flash_attention_kept(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                             float* part_o, float* part_ml, const int* positions, const int* cu_q,
+                                             const int* block_table, int table_stride, const int* tile_req,
+                                             const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
+                                             float scale, int window, int keep_first, int mode, int TT, int GH,
+                                             int head_chunks, int split_keys, int n_splits, long long n_pages,
+                                             int* err, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && mode == 1 && n_splits < 2)) return (int)cudaErrorInvalidValue;
     const int rows = mode == 0 ? 64 : 16;
     if (K <= 0 || H % K || TT <= 0 || GH <= 0 || TT * GH > rows || head_chunks * GH < H / K || bs <= 0)
         return (int)cudaErrorInvalidValue;
@@ -717,11 +746,24 @@ RLLM_API int rllm_paged_flash_attention(const void* q, const void* k_cache, cons
     p.tile_req = tile_req; p.tile_tok0 = tile_tok0; p.table_stride = table_stride;
     p.n_pages = (int)(n_pages > 0x7fffffffLL ? 0x7fffffffLL : n_pages); p.err = err;
     p.H = H; p.K = K; p.bs = bs; p.window = window; p.TT = TT; p.GH = GH; p.head_chunks = head_chunks;
+    p.keep_first = window > 0 ? keep_first : 0;
     p.split_keys = mode == 0 ? 0 : split_keys; p.part_rows = TT * GH;
     p.scale_log2 = scale * 1.4426950408889634f;
     if (hd == 128) return launch_flash<128>(p, mode, n_tiles, n_splits, stream);
     if (hd == 64) return launch_flash<64>(p, mode, n_tiles, n_splits, stream);
     return (int)cudaErrorInvalidValue;
+}
+
+RLLM_API int rllm_paged_flash_attention(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                        float* part_o, float* part_ml, const int* positions, const int* cu_q,
+                                        const int* block_table, int table_stride, const int* tile_req,
+                                        const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
+                                        float scale, int window, int mode, int TT, int GH, int head_chunks,
+                                        int split_keys, int n_splits, long long n_pages, int* err,
+                                        cudaStream_t stream) {
+    return rllm_paged_flash_attention_kept(q, k_cache, v_cache, out, part_o, part_ml, positions, cu_q, block_table,
+                                           table_stride, tile_req, tile_tok0, n_tiles, H, K, hd, bs, scale, window, 0,
+                                           mode, TT, GH, head_chunks, split_keys, n_splits, n_pages, err, stream);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -781,3 +823,4 @@ RLLM_API int rllm_paged_flash_decode_static(const void* q, const void* k_cache, 
 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_paged_flash_attention)
+RLLM_PACKED(rllm_paged_flash_attention_kept)

@@ -424,7 +424,8 @@ def qkv_rownorm_store(qkv, bias, q_norm_w, k_norm_w, slots, q_out, k_cache, v_ca
     """Biased q/k/v row -> RMSNorm over the whole q row and the whole k row (weights per column, None:
     no norm) -> queries out, keys and values into the paged cache; see rowwise.cu."""
     _need_cuda(qkv, bias, q_norm_w, k_norm_w, slots, q_out, k_cache, v_cache)
-    _need_contig(qkv=qkv, q_out=q_out, k_cache=k_cache, v_cache=v_cache, slots=slots)
+    _need_contig(q_out=q_out, k_cache=k_cache, v_cache=v_cache, slots=slots)
+    _rows2d(qkv, "qkv")                       # may be the leading columns of a wider projection
     n = qkv.shape[0]
     assert qkv.shape[1] == H * dk + G * dk + G * dv and q_out.shape == (n, H * dk)
     assert slots.dtype == torch.int32 and slots.numel() == n
@@ -433,7 +434,8 @@ def qkv_rownorm_store(qkv, bias, q_norm_w, k_norm_w, slots, q_out, k_cache, v_ca
     for w, size in ((bias, qkv.shape[1]), (q_norm_w, H * dk), (k_norm_w, G * dk)):
         assert w is None or (w.dtype == torch.float32 and w.numel() == size and w.is_contiguous())
     _check(core().rllm_qkv_rownorm_store(
-        _ptr(qkv), c_int(_code(qkv)), _ptr(bias), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(slots), _ptr(q_out),
+        _ptr(qkv), c_int(_code(qkv)), c_longlong(qkv.stride(0)), _ptr(bias), _ptr(q_norm_w), _ptr(k_norm_w),
+        _ptr(slots), _ptr(q_out),
         _ptr(k_cache), _ptr(v_cache), c_int(_code(q_out)), c_int(n), c_int(H), c_int(G), c_int(dk), c_int(dv),
         c_int(block_size), c_float(eps), c_int(1 if write_kv else 0), c_longlong(k_cache.shape[0] * block_size),
         _ptr(error_word(qkv.device)), _stream()), "qkv_rownorm_store")
@@ -1161,9 +1163,12 @@ class AttentionPlan:
 
 def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0,
                           n_tiles, H, K, hd, block_size, scale, window, mode, TT, GH, head_chunks,
-                          split_keys=DECODE_SPLIT_KEYS, n_splits=1):
+                          split_keys=DECODE_SPLIT_KEYS, n_splits=1, keep_first=0):
     """Tensor-core paged attention; mode 0: prefill shape, mode 1: decode shape with split keys
-    (allocates the partials as scratch).  See attention_flash.cu."""
+    (allocates the partials as scratch).  keep_first (with a window): the first keys of a request stay
+    visible; in mode 1 one split more, the last, is theirs.  See attention_flash.cu."""
+    if keep_first and window and mode == 1:
+        n_splits += 1
     _need_cuda(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0)
     _need_contig(q=q, k_cache=k_cache, v_cache=v_cache, out=out)
     if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS:
@@ -1174,12 +1179,13 @@ def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table
         rows = n_tiles * K * head_chunks * n_splits * TT * GH
         part_o = torch.empty(rows * hd, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
-    _check(_lib("attn").rllm_paged_flash_attention(
+    _check(_lib("attn").rllm_paged_flash_attention_kept(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(positions),
         _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req), _ptr(tile_tok0),
         c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale), c_int(window),
-        c_int(mode), c_int(TT), c_int(GH), c_int(head_chunks), c_int(split_keys), c_int(n_splits),
-        c_longlong(k_cache.shape[0]), _ptr(error_word(q.device)), _stream()), "paged_flash_attention")
+        c_int(keep_first if window else 0), c_int(mode), c_int(TT), c_int(GH), c_int(head_chunks), c_int(split_keys),
+        c_int(n_splits), c_longlong(k_cache.shape[0]), _ptr(error_word(q.device)), _stream()),
+        "paged_flash_attention")
     global _launches
     if mode == 1:
         _launches += 1                         # the combine kernel
@@ -1215,25 +1221,26 @@ def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_
                     keep_first=0, v_head_dim=None):
     """Attention of the step's tokens over the paged cache; chooses the kernel by element type,
     head size and the shape of the step (`ctx`: the step's StepContext).  float32, head sizes
-    other than 64 and 128, value heads of another size than the key heads and windows that keep
-    the first keys take the plain kernel."""
+    other than 64 and 128 and value heads of another size than the key heads take the plain kernel;
+    windows that keep the first keys take the mma.sync kernels, not the tcgen05 one."""
     hdv = hd if not v_head_dim else int(v_head_dim)
-    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd or (keep_first and window):
+    keep_first = keep_first if window else 0
+    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd:
         return paged_attention_generic(q, k_cache, v_cache, out, ctx.positions, ctx.seq_ids, block_table,
                                        H, K, hd, block_size, scale, window, keep_first, hdv)
     key = (H // K, window)
     plan = ctx.plans.get(key)
     if plan is None:
         plan = ctx.plans[key] = AttentionPlan(ctx, H, K, window, q.device)
-    if plan.n_pre and plan.n_tc and USE_ATTENTION_TC and attention_tc_ok(q, hd, block_size, H, K):
+    if plan.n_pre and plan.n_tc and USE_ATTENTION_TC and attention_tc_ok(q, hd, block_size, H, K) and not keep_first:
         attention_tc(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.t_req, plan.t_tok,
                      plan.n_tc, H, K, hd, block_size, scale, window)
     elif plan.n_pre:
         paged_flash_attention(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.p_req,
                               plan.p_tok, plan.n_pre, H, K, hd, block_size, scale, window, 0, plan.TTp,
-                              plan.GHp, plan.chunks_p)
+                              plan.GHp, plan.chunks_p, keep_first=keep_first)
     if plan.n_dec:
         paged_flash_attention(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.d_req,
                               plan.d_tok, plan.n_dec, H, K, hd, block_size, scale, window, 1, plan.TTd,
-                              plan.GHd, plan.chunks_d, DECODE_SPLIT_KEYS, plan.n_splits)
+                              plan.GHd, plan.chunks_d, DECODE_SPLIT_KEYS, plan.n_splits, keep_first=keep_first)
     return out

@@ -92,7 +92,8 @@ RLLM_API int rllm_cat2_cast(const float* x, const void* delta, int delta_dt, flo
                        delta_dt, s, y, out, out_dt, d, total);
 }
 
-// One block per token.  qkv[t] = [q (wq) | k (wk) | v (wv)] (+ bias); q and k rows are divided by
+// One block per token.  qkv[t] = [q (wq) | k (wk) | v (wv) | ...] with rows `ld` apart (the projection
+// may hold more columns behind v, an output gate for instance) (+ bias); q and k rows are divided by
 // their root mean square over the whole row (eps inside the root) and multiplied by a weight per
 // column when the weight is given; q -> q_out[t]; k, v -> the paged cache at slots[t]
 // (layouts [page][kv_head][bs][dk] and [page][kv_head][bs][dv]); slot < 0 writes nothing, a slot
@@ -101,13 +102,13 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 qkv_rownorm_store_kernel(const TI* qkv, const float* __restrict__ bias, const float* __restrict__ q_norm_w,
                          const float* __restrict__ k_norm_w, const int* __restrict__ slots, TO* q_out, TO* k_cache,
-                         TO* v_cache, int wq, int wk, int wv, int G, int dk, int dv, int bs, float eps,
+                         TO* v_cache, long long ld, int wq, int wk, int wv, int G, int dk, int dv, int bs, float eps,
                          int write_kv, int n_slots, int* err) {
     __shared__ float red[33];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, tid = threadIdx.x;
-    const TI* row = qkv + (size_t)t * (wq + wk + wv);
+    const TI* row = qkv + (size_t)t * ld;
     float sq = 0.f, sk = 0.f;
     for (int c = tid; c < wq; c += blockDim.x) {
         const float v = to_f<TI>(row[c]) + (bias ? bias[c] : 0.f);
@@ -145,16 +146,17 @@ qkv_rownorm_store_kernel(const TI* qkv, const float* __restrict__ bias, const fl
     }
 }
 
-RLLM_API int rllm_qkv_rownorm_store(const void* qkv, int in_dt, const float* bias, const float* q_norm_w,
+RLLM_API int rllm_qkv_rownorm_store(const void* qkv, int in_dt, long long ld, const float* bias, const float* q_norm_w,
                                     const float* k_norm_w, const int* slots, void* q_out, void* k_cache,
                                     void* v_cache, int out_dt, int n, int H, int G, int dk, int dv, int bs,
                                     float eps, int write_kv, long long n_slots, int* err, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || bs <= 0) return (int)cudaErrorInvalidValue;
+    if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || bs <= 0 || ld < (long long)H * dk + (long long)G * (dk + dv))
+        return (int)cudaErrorInvalidValue;
     const int ns = (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots);
 #define LAUNCH(TI, TO)                                                                                         \
     return rllm_launch(qkv_rownorm_store_kernel<TI, TO>, dim3(n), dim3(256), 0, stream, (const TI*)qkv, bias,  \
-                       q_norm_w, k_norm_w, slots, (TO*)q_out, (TO*)k_cache, (TO*)v_cache, H * dk, G * dk, G * dv, \
+                       q_norm_w, k_norm_w, slots, (TO*)q_out, (TO*)k_cache, (TO*)v_cache, ld, H * dk, G * dk, G * dv, \
                        G, dk, dv, bs, eps, write_kv, ns, err)
     if (in_dt == RLLM_F32 && out_dt == RLLM_F32) { LAUNCH(float, float); }
     if (in_dt == RLLM_F32 && out_dt == RLLM_BF16) { LAUNCH(float, bf16); }

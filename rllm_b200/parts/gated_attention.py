@@ -14,7 +14,7 @@ For normed input rows h [n, d] (H query heads, G key/value heads, key size dk, v
 Parameters: hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim, bias, qk_norm ("row" or
 None), eps, window (0: all keys), keep_first, scale, gate ("sigmoid" or None).  Tensors under
 <prefix>: q, k, v, o, g and, by the options, q.b, k.b, v.b, q.norm, k.norm.  Load-time transform:
-q, k and v (and their biases) are stacked into one projection.  Scores, softmax, norms and the
+q, k, v and the gate are stacked into one projection [q | k | v | g] (the biases of q, k, v likewise).  Scores, softmax, norms and the
 gate's sigmoid are float32 in every mode.
 """
 from __future__ import annotations
@@ -51,7 +51,7 @@ class GatedWindowAttention(Mixer):
             raise PartError(f"gated_attention: gate {self.gate!r} is not supported")
         if max(self.dk, self.dv) > 512:
             raise PartError("gated_attention: head sizes up to 512")
-        self.w_qkv = self.b_qkv = self.q_norm_w = self.k_norm_w = self.w_g = self.w_o = None
+        self.w_qkv = self.b_qkv = self.q_norm_w = self.k_norm_w = self.w_o = None
 
     def cache_need(self):
         return PagedKVNeed(self.G, self.dk, self.window, self.keep_first, self.dv if self.dv != self.dk else 0)
@@ -71,20 +71,21 @@ class GatedWindowAttention(Mixer):
 
     def load(self, tensors):
         p, dt = self.prefix, self.runtime.dtype
-        self.w_qkv = self._to_device(torch.cat([tensors[p + n].to(dt) for n in "qkv"], 0))
+        names = "qkvg" if self.gate else "qkv"
+        self.w_qkv = self._to_device(torch.cat([tensors[p + n].to(dt) for n in names], 0))
         if self.bias:
             self.b_qkv = self._to_device(torch.cat([tensors[p + n + ".b"].to(torch.float32) for n in "qkv"], 0),
                                          torch.float32)
         if self.qk_norm:
             self.q_norm_w = self._to_device(tensors[p + "q.norm"], torch.float32)
             self.k_norm_w = self._to_device(tensors[p + "k.norm"], torch.float32)
-        if self.gate:
-            self.w_g = self._to_device(tensors[p + "g"])
         self.w_o = self._to_device(tensors[p + "o"])
 
     def forward(self, h, ctx, cache, position=None, residual=None):
         n, dt, dev = h.shape[0], self.runtime.dtype, h.device
-        qkv = ops.linear(h, self.w_qkv, out_dtype=torch.float32)
+        wide = ops.linear(h, self.w_qkv, out_dtype=torch.float32)          # [q | k | v | gate]
+        n_qkv = self.H * self.dk + self.G * (self.dk + self.dv)
+        qkv = wide[:, :n_qkv]
         q = torch.empty((n, self.H * self.dk), dtype=dt, device=dev)
         ops.qkv_rownorm_store(qkv, self.b_qkv, self.q_norm_w, self.k_norm_w, cache.slots, q, cache.k, cache.v,
                               self.H, self.G, self.dk, self.dv, cache.block_size, self.eps, write_kv=cache.write)
@@ -92,6 +93,5 @@ class GatedWindowAttention(Mixer):
         ops.paged_attention(q, cache.k, cache.v, attn, ctx, cache.block_table, self.H, self.G, self.dk,
                             cache.block_size, self.scale, self.window, self.keep_first, self.dv)
         if self.gate:
-            g = ops.linear(h, self.w_g, out_dtype=torch.float32)
-            ops.rows_act(attn, attn, mul=g, mul_act=self.gate)
+            ops.rows_act(attn, attn, mul=wide[:, n_qkv:], mul_act=self.gate)
         return ops.linear(attn, self.w_o, out_dtype=torch.float32)
