@@ -66,26 +66,37 @@ RLLM_API int rllm_conv_silu(const float* xz, long long ld, const float* w, const
 //   y  = sum_n S[c, n] * C[t, n] + D[c] * x[t, c];      out[t, c] = y * silu(z[t, c])
 // x: the convolution's output (activation type), B and C: columns of `low` (float32), z: columns
 // [inner, 2 inner) of xz.  SCAN_LANES lanes share a channel (state index n = lane + SCAN_LANES * k);
-// their partial sums are added in a fixed butterfly.  At the end the convolution's kept inputs
-// move on by this step's tokens.
+// their partial sums are added in a fixed butterfly.  A block owns SCAN_CH channels of one request and
+// walks its tokens SCAN_TOK at a time: x, the step sizes (softplus done on the way in), silu(z), B and
+// C of a chunk lie in shared memory, and the next chunk's values are already on their way from global
+// memory (held in registers) while this one is worked through, so the recurrence never waits for a
+// load.  At the end the convolution's kept inputs move on by this step's tokens.
 #define SCAN_LANES 4
 #define SCAN_CH 32            // channels per block (128 threads)
-#define SCAN_TOK 8            // tokens whose B and C are staged in shared memory at a time
+#define SCAN_TOK 16           // tokens per chunk
+#define SCAN_THREADS (SCAN_LANES * SCAN_CH)
 
 template <typename TA, int NPT>
-__global__ void __launch_bounds__(SCAN_LANES * SCAN_CH)
+__global__ void __launch_bounds__(SCAN_THREADS)
 selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float* low, long long ld_low, int b_off,
                       int c_off, const float* dtr, const float* __restrict__ dt_b, const float* __restrict__ A,
                       const float* __restrict__ Dp, float* state, long long slot_stride, long long conv_off,
                       const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int inner, int N,
                       int taps) {
-    extern __shared__ float bc[];                       // [SCAN_TOK][2][N]
+    constexpr int PRE_X = 3 * SCAN_TOK * SCAN_CH / SCAN_THREADS;      // x, dt, z of a chunk: values per thread
+    constexpr int PRE_BC = NPT;                                        // B and C of a chunk (N <= SCAN_LANES * NPT)
+    extern __shared__ float sm_scan[];
+    float* s_x = sm_scan;                                // [SCAN_TOK][SCAN_CH]
+    float* s_dt = s_x + SCAN_TOK * SCAN_CH;
+    float* s_z = s_dt + SCAN_TOK * SCAN_CH;              // silu(z)
+    float* s_bc = s_z + SCAN_TOK * SCAN_CH;              // [SCAN_TOK][2][N]
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.y;
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
-    const int lane = threadIdx.x % SCAN_LANES;
-    const int c_own = blockIdx.x * SCAN_CH + threadIdx.x / SCAN_LANES;
+    const int tid = threadIdx.x, lane = tid % SCAN_LANES, cl = tid / SCAN_LANES;
+    const int c_base = blockIdx.x * SCAN_CH;
+    const int c_own = c_base + cl;
     const bool live = c_own < inner;
     const int c = live ? c_own : inner - 1;             // lanes beyond the last channel shadow it and write nothing
     float* st = state + (size_t)slots[r] * slot_stride;
@@ -97,21 +108,61 @@ selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float
         S[k] = on ? st[(size_t)c * N + n] : 0.f;
         a[k] = on ? A[(size_t)c * N + n] : 0.f;
     }
-    const float db = dt_b[c], dd = Dp[c];
+    const float dd = Dp[c];
+    float px[PRE_X], pbc[PRE_BC];
+    // element e of the x/dt/z part: which (0 x, 1 dt, 2 z), token, channel of the block
+    auto fetch = [&](int tb) {
+        const int nt = min(SCAN_TOK, t1 - tb);
+#pragma unroll
+        for (int i = 0; i < PRE_X; ++i) {
+            const int e = tid + i * SCAN_THREADS;
+            const int which = e / (SCAN_TOK * SCAN_CH), rem = e % (SCAN_TOK * SCAN_CH);
+            const int tt = rem / SCAN_CH, ch = c_base + rem % SCAN_CH;
+            float v = 0.f;
+            if (tt < nt && ch < inner) {
+                const size_t t = tb + tt;
+                v = which == 0 ? to_f<TA>(x[t * inner + ch]) : which == 1 ? dtr[t * inner + ch] : xz[t * ld_xz + inner + ch];
+            }
+            px[i] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < PRE_BC; ++i) {
+            const int e = tid + i * SCAN_THREADS;
+            const int tt = e / (2 * N), j = e % (2 * N);
+            pbc[i] = (tt < nt) ? low[(size_t)(tb + tt) * ld_low + (j < N ? b_off + j : c_off + j - N)] : 0.f;
+        }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int i = 0; i < PRE_X; ++i) {
+            const int e = tid + i * SCAN_THREADS;
+            const int which = e / (SCAN_TOK * SCAN_CH), rem = e % (SCAN_TOK * SCAN_CH);
+            const int ch = c_base + rem % SCAN_CH;
+            float v = px[i];
+            if (which == 1) v = softplus_f(v + (ch < inner ? dt_b[ch] : 0.f));
+            else if (which == 2) v = silu_f(v);
+            sm_scan[e] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < PRE_BC; ++i) {
+            const int e = tid + i * SCAN_THREADS;
+            if (e < SCAN_TOK * 2 * N) s_bc[e] = pbc[i];
+        }
+    };
+    if (t0 < t1) {
+        fetch(t0);
+        stash();
+    }
+    __syncthreads();
     for (int tb = t0; tb < t1; tb += SCAN_TOK) {
         const int nt = min(SCAN_TOK, t1 - tb);
-        __syncthreads();
-        for (int i = threadIdx.x; i < nt * 2 * N; i += blockDim.x) {
-            const int tt = i / (2 * N), j = i % (2 * N);
-            bc[i] = low[(size_t)(tb + tt) * ld_low + (j < N ? b_off + j : c_off + j - N)];
-        }
-        __syncthreads();
+        const bool more = tb + SCAN_TOK < t1;
+        if (more) fetch(tb + SCAN_TOK);
         for (int tt = 0; tt < nt; ++tt) {
-            const size_t t = tb + tt;
-            const float xv = to_f<TA>(x[t * inner + c]);
-            const float dt = softplus_f(dtr[t * inner + c] + db);
+            const float xv = s_x[tt * SCAN_CH + cl];
+            const float dt = s_dt[tt * SCAN_CH + cl];
             const float dx = dt * xv;
-            const float* Bt = bc + tt * 2 * N;
+            const float* Bt = s_bc + tt * 2 * N;
             const float* Ct = Bt + N;
             float part = 0.f;
 #pragma unroll
@@ -124,11 +175,12 @@ selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float
             }
             part += __shfl_xor_sync(0xffffffffu, part, 1);
             part += __shfl_xor_sync(0xffffffffu, part, 2);
-            if (lane == 0 && live) {
-                const float z = xz[t * ld_xz + inner + c];
-                out[t * inner + c] = from_f<TA>((part + dd * xv) * silu_f(z));
-            }
+            if (lane == 0 && live)
+                out[(size_t)(tb + tt) * inner + c] = from_f<TA>((part + dd * xv) * s_z[tt * SCAN_CH + cl]);
         }
+        __syncthreads();                                 // everyone is done with this chunk
+        if (more) stash();
+        __syncthreads();
     }
     if (!live) return;
 #pragma unroll
@@ -154,8 +206,8 @@ RLLM_API int rllm_selective_scan(const void* x, int act_dt, const float* xz, lon
                                  int inner, int N, int taps, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (N <= 0 || N > SCAN_LANES * 64 || inner <= 0 || taps < 1) return (int)cudaErrorInvalidValue;
-    const dim3 grid((inner + SCAN_CH - 1) / SCAN_CH, n_requests), block(SCAN_LANES * SCAN_CH);
-    const size_t smem = (size_t)SCAN_TOK * 2 * N * sizeof(float);
+    const dim3 grid((inner + SCAN_CH - 1) / SCAN_CH, n_requests), block(SCAN_THREADS);
+    const size_t smem = (size_t)(3 * SCAN_TOK * SCAN_CH + SCAN_TOK * 2 * N) * sizeof(float);
 #define LAUNCH(TA, NPT)                                                                                          \
     return rllm_launch(selective_scan_kernel<TA, NPT>, grid, block, smem, stream, (const TA*)x, xz, ld_xz, low,  \
                        ld_low, b_off, c_off, dtr, dt_b, A, Dp, state, slot_stride, conv_off, cu_q, slots, (TA*)out, \
@@ -209,91 +261,144 @@ RLLM_API int rllm_token_shift(const void* h, int act_dt, const float* mu, const 
 }
 
 // ------------------------------------------------------------------ WKV with data-dependent decay
-// One block per (request, head); thread j owns column j of the head's state S [D keys][D values].
-// Per token, with r, k, v the head's rows of the projections, w = exp(-exp(wraw + w0)) the decay
-// per key channel and u the bonus of the current token:
+// One block per (request, head).  Per token, with r, k, v the head's rows of the projections,
+// w = exp(-exp(wraw + w0)) the decay per key channel and u the bonus of the current token:
 //   o[j] = sum_i r[i] * (S[i][j] + u[i] * k[i] * v[j]);     S[i][j] = w[i] * S[i][j] + k[i] * v[j]
 // then o is divided by its root mean square over the head (eps inside the root), multiplied by the
-// norm weight and by silu(gate), and stored in the activation type.  Tokens are taken WKV_TOK at a
-// time: r, k and w of the chunk go through shared memory, the outputs too, and the unit norms of
-// the chunk are worked out by the warps in turn.  The kept previous row moves on at the end.
-#define WKV_TOK 8
+// norm weight and by silu(gate), and stored in the activation type.
+// WKV_PARTS neighbouring lanes share a value channel j: each holds a quarter of column j of the state
+// (DMAX / 4 key channels) in registers, and their partial sums of o[j] are added in a fixed
+// butterfly.  Tokens are taken WKV_TOK at a time: r, k, the decay (exponentials done on the way in),
+// v and the gate of a chunk lie in shared memory (rows padded with zeros to DMAX, read four at a
+// time), the next chunk's values are already on their way from global memory (held in registers)
+// while this one is worked through, and the chunk's outputs are normalised by the warps in turn.
+// The kept previous row moves on at the end.
+#define WKV_TOK 16
+#define WKV_PARTS 4
 
 template <typename TA, int DMAX>
-__global__ void __launch_bounds__(DMAX)
+__global__ void __launch_bounds__(WKV_PARTS * DMAX)
 wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw, const float* gp, long long ld,
            const float* __restrict__ w0, const float* __restrict__ u, const float* __restrict__ norm_w, float eps,
            float* state, long long slot_stride, long long prev_off, const TA* h, int width,
            const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int H, int D) {
-    extern __shared__ float sm[];                        // r, k, w: [3][WKV_TOK][D]; o: [WKV_TOK][D]; u: [D]
-    float* s_r = sm;
-    float* s_k = s_r + WKV_TOK * D;
-    float* s_w = s_k + WKV_TOK * D;
-    float* s_o = s_w + WKV_TOK * D;
-    float* s_u = s_o + WKV_TOK * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) s_u[i] = u[(size_t)blockIdx.x * D + i];
+    constexpr int IPT = DMAX / WKV_PARTS;               // key channels per thread
+    constexpr int NT = WKV_PARTS * DMAX;                // threads
+    constexpr int TD = WKV_TOK * DMAX;
+    constexpr int PRE = 5 * TD / NT;                    // values a thread brings in per chunk
+    extern __shared__ __align__(16) float sm_wkv[];      // r, k, w, v, gate: [5][WKV_TOK][DMAX]; o: [WKV_TOK][DMAX]; u: [DMAX]
+    float* s_r = sm_wkv;
+    float* s_k = s_r + TD;
+    float* s_w = s_k + TD;
+    float* s_v = s_w + TD;
+    float* s_g = s_v + TD;
+    float* s_o = s_g + TD;
+    float* s_u = s_o + TD;
+    const int tid = threadIdx.x, j = tid / WKV_PARTS, part = tid % WKV_PARTS;
+    const int head = blockIdx.x, r = blockIdx.y;
+    const size_t col = (size_t)head * D;
+    for (int i = tid; i < DMAX; i += NT) s_u[i] = i < D ? u[col + i] : 0.f;
     pdl_wait();
     pdl_launch_dependents();
-    const int r = blockIdx.y, head = blockIdx.x, j = threadIdx.x;
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     float* st = state + (size_t)slots[r] * slot_stride;
     float* Sg = st + (size_t)head * D * D;
     const bool live = j < D;
-    float S[DMAX];
+    const int i0 = part * IPT;
+    float S[IPT];
 #pragma unroll
-    for (int i = 0; i < DMAX; ++i) S[i] = (live && i < D) ? Sg[(size_t)i * D + j] : 0.f;
-    const size_t col = (size_t)head * D;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int ii = 0; ii < IPT; ++ii) S[ii] = (live && i0 + ii < D) ? Sg[(size_t)(i0 + ii) * D + j] : 0.f;
+    float pre[PRE];
+    auto fetch = [&](int tb) {
+        const int nt = min(WKV_TOK, t1 - tb);
+#pragma unroll
+        for (int x = 0; x < PRE; ++x) {
+            const int e = tid + x * NT;
+            const int arr = e / TD, rem = e % TD, tt = rem / DMAX, cc = rem % DMAX;
+            const float* src = arr == 0 ? rp : arr == 1 ? kp : arr == 2 ? wraw : arr == 3 ? vp : gp;
+            pre[x] = (tt < nt && cc < D) ? src[(size_t)(tb + tt) * ld + col + cc] : 0.f;
+        }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int x = 0; x < PRE; ++x) {
+            const int e = tid + x * NT;
+            const int arr = e / TD, cc = e % DMAX;
+            float v = pre[x];
+            if (arr == 2) v = cc < D ? expf(-expf(v + w0[col + cc])) : 0.f;
+            sm_wkv[e] = v;
+        }
+    };
+    if (t0 < t1) {
+        fetch(t0);
+        stash();
+    }
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31;
+    constexpr int n_warps = NT / 32;
     for (int tb = t0; tb < t1; tb += WKV_TOK) {
         const int nt = min(WKV_TOK, t1 - tb);
-        __syncthreads();
-        for (int i = threadIdx.x; i < nt * D; i += blockDim.x) {
-            const int tt = i / D, cc = i % D;
-            const size_t g = (size_t)(tb + tt) * ld + col + cc;
-            s_r[i] = rp[g];
-            s_k[i] = kp[g];
-            s_w[i] = expf(-expf(wraw[g] + w0[col + cc]));
-        }
-        __syncthreads();
-        if (live) {
-            for (int tt = 0; tt < nt; ++tt) {
-                const float vj = vp[(size_t)(tb + tt) * ld + col + j];
-                const float* rr = s_r + tt * D;
-                const float* kk = s_k + tt * D;
-                const float* ww = s_w + tt * D;
-                float o = 0.f;
+        const bool more = tb + WKV_TOK < t1;
+        if (more) fetch(tb + WKV_TOK);
+        for (int tt = 0; tt < nt; ++tt) {
+            const float vj = s_v[tt * DMAX + j];
+            const float4* r4 = reinterpret_cast<const float4*>(s_r + tt * DMAX + i0);
+            const float4* k4 = reinterpret_cast<const float4*>(s_k + tt * DMAX + i0);
+            const float4* w4 = reinterpret_cast<const float4*>(s_w + tt * DMAX + i0);
+            const float4* u4 = reinterpret_cast<const float4*>(s_u + i0);
+            float o = 0.f;
 #pragma unroll
-                for (int i = 0; i < DMAX; ++i) {
-                    if (i < D) {
-                        const float kv = kk[i] * vj;
-                        o += rr[i] * (S[i] + s_u[i] * kv);
-                        S[i] = ww[i] * S[i] + kv;
-                    }
-                }
-                s_o[tt * D + j] = o;
+            for (int q = 0; q < IPT / 4; ++q) {
+                const float4 rr = r4[q], kk = k4[q], ww = w4[q], uu = u4[q];
+                float kv;
+                kv = kk.x * vj; o += rr.x * (S[4 * q] + uu.x * kv); S[4 * q] = ww.x * S[4 * q] + kv;
+                kv = kk.y * vj; o += rr.y * (S[4 * q + 1] + uu.y * kv); S[4 * q + 1] = ww.y * S[4 * q + 1] + kv;
+                kv = kk.z * vj; o += rr.z * (S[4 * q + 2] + uu.z * kv); S[4 * q + 2] = ww.z * S[4 * q + 2] + kv;
+                kv = kk.w * vj; o += rr.w * (S[4 * q + 3] + uu.w * kv); S[4 * q + 3] = ww.w * S[4 * q + 3] + kv;
             }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (part == 0) s_o[tt * DMAX + j] = o;
         }
         __syncthreads();
         for (int tt = warp; tt < nt; tt += n_warps) {
             float ss = 0.f;
-            for (int i = lane; i < D; i += 32) ss += s_o[tt * D + i] * s_o[tt * D + i];
+            for (int i = lane; i < D; i += 32) ss += s_o[tt * DMAX + i] * s_o[tt * DMAX + i];
             const float rs = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
-            for (int i = lane; i < D; i += 32) {
-                const size_t g = (size_t)(tb + tt) * ld + col + i;
+            for (int i = lane; i < D; i += 32)
                 out[(size_t)(tb + tt) * H * D + col + i] =
-                    from_f<TA>(s_o[tt * D + i] * rs * norm_w[col + i] * silu_f(gp[g]));
-            }
+                    from_f<TA>(s_o[tt * DMAX + i] * rs * norm_w[col + i] * silu_f(s_g[tt * DMAX + i]));
         }
+        __syncthreads();                                 // everyone is done with this chunk
+        if (more) stash();
+        __syncthreads();
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < DMAX; ++i)
-            if (i < D) Sg[(size_t)i * D + j] = S[i];
+        for (int ii = 0; ii < IPT; ++ii)
+            if (i0 + ii < D) Sg[(size_t)(i0 + ii) * D + j] = S[ii];
     }
     if (head == 0 && t1 > t0) {
         float* pv = st + prev_off;
-        for (int c = threadIdx.x; c < width; c += blockDim.x) pv[c] = to_f<TA>(h[(size_t)(t1 - 1) * width + c]);
+        for (int c = tid; c < width; c += NT) pv[c] = to_f<TA>(h[(size_t)(t1 - 1) * width + c]);
     }
+}
+
+template <typename TA, int DMAX>
+static int launch_wkv(dim3 grid, size_t smem, cudaStream_t stream, const float* rp, const float* kp, const float* vp,
+                      const float* wraw, const float* gp, long long ld, const float* w0, const float* u,
+                      const float* norm_w, float eps, float* state, long long slot_stride, long long prev_off,
+                      const void* h, int width, const int* cu_q, const int* slots, void* out, int H, int D) {
+    if (smem > 48 * 1024) {
+        static bool raised = false;                      // once per instantiation: more dynamic shared memory than the default
+        if (!raised) {
+            cudaError_t e = cudaFuncSetAttribute(wkv_kernel<TA, DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            raised = true;
+        }
+    }
+    return rllm_launch(wkv_kernel<TA, DMAX>, grid, dim3(WKV_PARTS * DMAX), smem, stream, rp, kp, vp, wraw, gp, ld, w0, u,
+                       norm_w, eps, state, slot_stride, prev_off, (const TA*)h, width, cu_q, slots, (TA*)out, H, D);
 }
 
 RLLM_API int rllm_wkv(const float* rp, const float* kp, const float* vp, const float* wraw, const float* gp,
@@ -304,15 +409,16 @@ RLLM_API int rllm_wkv(const float* rp, const float* kp, const float* vp, const f
     if (n_requests <= 0) return 0;
     if (D <= 0 || D > 256 || H <= 0) return (int)cudaErrorInvalidValue;
     const dim3 grid(H, n_requests);
-    const size_t smem = (size_t)(4 * WKV_TOK + 1) * D * sizeof(float);
-#define LAUNCH(TA, DMAX)                                                                                       \
-    return rllm_launch(wkv_kernel<TA, DMAX>, grid, dim3(DMAX), smem, stream, rp, kp, vp, wraw, gp, ld, w0, u,  \
-                       norm_w, eps, state, slot_stride, prev_off, (const TA*)h, width, cu_q, slots, (TA*)out, H, D)
+    const int dmax = D <= 32 ? 32 : D <= 64 ? 64 : D <= 128 ? 128 : 256;
+    const size_t smem = (size_t)(6 * WKV_TOK + 1) * dmax * sizeof(float);
+#define LAUNCH(TA, DMAX)                                                                                        \
+    return launch_wkv<TA, DMAX>(grid, smem, stream, rp, kp, vp, wraw, gp, ld, w0, u, norm_w, eps, state, slot_stride, \
+                                prev_off, h, width, cu_q, slots, out, H, D)
 #define BY_D(TA)                                                                                               \
     do {                                                                                                       \
-        if (D <= 32) { LAUNCH(TA, 32); }                                                                       \
-        if (D <= 64) { LAUNCH(TA, 64); }                                                                       \
-        if (D <= 128) { LAUNCH(TA, 128); }                                                                     \
+        if (dmax == 32) { LAUNCH(TA, 32); }                                                                    \
+        if (dmax == 64) { LAUNCH(TA, 64); }                                                                    \
+        if (dmax == 128) { LAUNCH(TA, 128); }                                                                  \
         LAUNCH(TA, 256);                                                                                       \
     } while (0)
     if (act_dt == RLLM_F32) BY_D(float);
