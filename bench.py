@@ -155,6 +155,28 @@ def falalix_compare(a):
             V = model.spec.vocab_size
             eng = Engine(model, block_size=32, max_tokens=a.batch * (PROMPT + 256), max_requests=a.batch)
             prompts = [torch.randint(0, V, (PROMPT,), generator=g).tolist() for _ in range(a.batch)]
+            if a.profile:
+                # one step between cudaProfilerStart/Stop (ncu --profile-from-start off), no benchmark line
+                if name != "falalix":
+                    continue
+                if a.profile == "prefill":
+                    eng.step([StepItem("p", prompts[0], [PROMPT - 1])])
+                    eng.finish("p")
+                else:
+                    for b in range(a.batch):
+                        eng.step([StepItem(b, prompts[b], [])])
+                    for i in range(3):                                 # eager, capture, replay
+                        eng.step([StepItem(b, [1 + i], [0]) for b in range(a.batch)])
+                torch.cuda.synchronize()
+                torch.cuda.profiler.start()
+                if a.profile == "prefill":
+                    eng.step([StepItem("p", prompts[0], [PROMPT - 1])])
+                else:
+                    eng.step([StepItem(b, [7], [0]) for b in range(a.batch)])
+                torch.cuda.synchronize()
+                torch.cuda.profiler.stop()
+                print(f"profiled one {a.profile} step of the Falalix shape {size}")
+                return 0
             times = []
             for rep in range(4):                       # prefill of one prompt in one step; the first loads kernels
                 s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

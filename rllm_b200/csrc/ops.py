@@ -508,6 +508,13 @@ def token_shift(h, mu, state, prev_off, seq_ids, cu_q, slots, out):
     return out
 
 
+def wkv_state_floats(H: int, D: int) -> int:
+    """Floats of a request's WKV state (the kernel keeps each head's state padded to a power of two
+    and in its threads' order; recurrent.cu).  No device needed."""
+    dmax = 32 if D <= 32 else 64 if D <= 64 else 128 if D <= 128 else 256
+    return H * dmax * dmax
+
+
 def wkv(r, k, v, wraw, g, w0, u, norm_w, eps, state, prev_off, h, cu_q, slots, out, n_requests, H, D):
     """The RWKV recurrence with data-dependent decay, unit norm per head, norm weight and silu gate; see
     recurrent.cu.  r, k, v, wraw, g float32 [n, H*D] (equal row strides); out activation type."""
@@ -523,7 +530,7 @@ def wkv(r, k, v, wraw, g, w0, u, norm_w, eps, state, prev_off, h, cu_q, slots, o
     if D > 256:
         raise KernelError(f"head size {D} exceeds the WKV kernel's limit of 256")
     st = _state2d(state)
-    assert prev_off >= H * D * D and prev_off + h.shape[1] <= st.shape[1]
+    assert prev_off >= wkv_state_floats(H, D) and prev_off + h.shape[1] <= st.shape[1]
     _check(_lib("recur").rllm_wkv(_ptr(r), _ptr(k), _ptr(v), _ptr(wraw), _ptr(g), c_longlong(r.stride(0)), _ptr(w0),
                                   _ptr(u), _ptr(norm_w), c_float(eps), _ptr(st), c_longlong(st.stride(0)),
                                   c_longlong(prev_off), _ptr(h), c_int(_code(h)), c_int(h.shape[1]), _ptr(cu_q),

@@ -10,7 +10,10 @@
 //
 // State slot layouts (floats):
 //   Mamba:  S [inner][N], then the last taps-1 inputs of the convolution [inner][taps-1] (oldest first)
-//   RWKV :  S [heads][D (key channel)][D (value channel)], then the previous token's input [width]
+//   RWKV :  S of every head, DMAX * DMAX floats a head (DMAX: the head size rounded up to 32, 64, 128
+//           or 256; rllm_wkv_state_floats) in the order in which the WKV kernel's threads hold it, so
+//           that a step reads and writes it in whole lines: value (register, thread) at register *
+//           threads + thread; then the previous token's input [width].  Nothing else reads S.
 #include "common.cuh"
 #include <math.h>
 
@@ -158,7 +161,9 @@ selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float
         const int nt = min(SCAN_TOK, t1 - tb);
         const bool more = tb + SCAN_TOK < t1;
         if (more) fetch(tb + SCAN_TOK);
-        for (int tt = 0; tt < nt; ++tt) {
+        // One token: only S carries over from the token before, so with the loop unrolled the
+        // exponentials, loads and shuffles of neighbouring tokens overlap.
+        auto token = [&](int tt) {
             const float xv = s_x[tt * SCAN_CH + cl];
             const float dt = s_dt[tt * SCAN_CH + cl];
             const float dx = dt * xv;
@@ -177,6 +182,12 @@ selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float
             part += __shfl_xor_sync(0xffffffffu, part, 2);
             if (lane == 0 && live)
                 out[(size_t)(tb + tt) * inner + c] = from_f<TA>((part + dd * xv) * s_z[tt * SCAN_CH + cl]);
+        };
+        if (nt == SCAN_TOK) {
+#pragma unroll 4
+            for (int tt = 0; tt < SCAN_TOK; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < nt; ++tt) token(tt);
         }
         __syncthreads();                                 // everyone is done with this chunk
         if (more) stash();
@@ -241,7 +252,7 @@ __global__ void token_shift_kernel(const TA* h, const float* __restrict__ mu, co
     const int r = seq_ids[t];
     const bool first = t == cu_q[r];
     const float* pv = state + (size_t)slots[r] * slot_stride + prev_off;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < d; c += gridDim.y * blockDim.x) {
         const float cur = to_f<TA>(h[(size_t)t * d + c]);
         const float prev = first ? pv[c] : to_f<TA>(h[(size_t)(t - 1) * d + c]);
         for (int s = 0; s < n_streams; ++s)
@@ -253,10 +264,12 @@ RLLM_API int rllm_token_shift(const void* h, int act_dt, const float* mu, const 
                               long long prev_off, const int* seq_ids, const int* cu_q, const int* slots, void* out,
                               int n, int d, int n_streams, cudaStream_t stream) {
     if (n <= 0) return 0;
+    // few tokens (a decode step): the row is spread over several blocks
+    const dim3 grid(n, n >= 256 ? 1 : (d + 255) / 256 > 32 ? 32 : (d + 255) / 256);
     if (act_dt == RLLM_F32)
-        return rllm_launch(token_shift_kernel<float>, dim3(n), dim3(256), 0, stream, (const float*)h, mu, state,
+        return rllm_launch(token_shift_kernel<float>, grid, dim3(256), 0, stream, (const float*)h, mu, state,
                            slot_stride, prev_off, seq_ids, cu_q, slots, (float*)out, n, d, n_streams);
-    return rllm_launch(token_shift_kernel<bf16>, dim3(n), dim3(256), 0, stream, (const bf16*)h, mu, state,
+    return rllm_launch(token_shift_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)h, mu, state,
                        slot_stride, prev_off, seq_ids, cu_q, slots, (bf16*)out, n, d, n_streams);
 }
 
@@ -265,28 +278,32 @@ RLLM_API int rllm_token_shift(const void* h, int act_dt, const float* mu, const 
 // w = exp(-exp(wraw + w0)) the decay per key channel and u the bonus of the current token:
 //   o[j] = sum_i r[i] * (S[i][j] + u[i] * k[i] * v[j]);     S[i][j] = w[i] * S[i][j] + k[i] * v[j]
 // then o is divided by its root mean square over the head (eps inside the root), multiplied by the
-// norm weight and by silu(gate), and stored in the activation type.
-// WKV_PARTS neighbouring lanes share a value channel j: each holds a quarter of column j of the state
-// (DMAX / 4 key channels) in registers, and their partial sums of o[j] are added in a fixed
+// norm weight and by silu(gate), and stored in the activation type.  The bonus term is the same
+// number for every value channel, o[j] = sum_i r[i] S[i][j] + (sum_i r[i] u[i] k[i]) * v[j], and is
+// worked out once per token.
+// A thread owns an eighth of the key channels (DMAX / 8) of two neighbouring value channels of the
+// state, in registers: r, k and w are read once for both columns (the kernel is bound by those
+// reads), and the WKV_PARTS lanes that share a pair of columns add their partial sums in a fixed
 // butterfly.  Tokens are taken WKV_TOK at a time: r, k, the decay (exponentials done on the way in),
 // v and the gate of a chunk lie in shared memory (rows padded with zeros to DMAX, read four at a
 // time), the next chunk's values are already on their way from global memory (held in registers)
 // while this one is worked through, and the chunk's outputs are normalised by the warps in turn.
 // The kept previous row moves on at the end.
 #define WKV_TOK 16
-#define WKV_PARTS 4
+#define WKV_PARTS 8
+#define WKV_COLS 2
 
 template <typename TA, int DMAX>
-__global__ void __launch_bounds__(WKV_PARTS * DMAX)
+__global__ void __launch_bounds__(WKV_PARTS * DMAX / WKV_COLS)
 wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw, const float* gp, long long ld,
            const float* __restrict__ w0, const float* __restrict__ u, const float* __restrict__ norm_w, float eps,
            float* state, long long slot_stride, long long prev_off, const TA* h, int width,
            const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int H, int D) {
     constexpr int IPT = DMAX / WKV_PARTS;               // key channels per thread
-    constexpr int NT = WKV_PARTS * DMAX;                // threads
+    constexpr int NT = WKV_PARTS * DMAX / WKV_COLS;     // threads
     constexpr int TD = WKV_TOK * DMAX;
     constexpr int PRE = 5 * TD / NT;                    // values a thread brings in per chunk
-    extern __shared__ __align__(16) float sm_wkv[];      // r, k, w, v, gate: [5][WKV_TOK][DMAX]; o: [WKV_TOK][DMAX]; u: [DMAX]
+    extern __shared__ __align__(16) float sm_wkv[];      // r, k, w, v, gate: [5][WKV_TOK][DMAX]; o: [WKV_TOK][DMAX]; u: [DMAX]; bonus: [WKV_TOK]
     float* s_r = sm_wkv;
     float* s_k = s_r + TD;
     float* s_w = s_k + TD;
@@ -294,7 +311,8 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
     float* s_g = s_v + TD;
     float* s_o = s_g + TD;
     float* s_u = s_o + TD;
-    const int tid = threadIdx.x, j = tid / WKV_PARTS, part = tid % WKV_PARTS;
+    float* s_c = s_u + DMAX;
+    const int tid = threadIdx.x, j0 = WKV_COLS * (tid / WKV_PARTS), part = tid % WKV_PARTS;
     const int head = blockIdx.x, r = blockIdx.y;
     const size_t col = (size_t)head * D;
     for (int i = tid; i < DMAX; i += NT) s_u[i] = i < D ? u[col + i] : 0.f;
@@ -302,12 +320,15 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
     pdl_launch_dependents();
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     float* st = state + (size_t)slots[r] * slot_stride;
-    float* Sg = st + (size_t)head * D * D;
-    const bool live = j < D;
+    float* Sg = st + (size_t)head * DMAX * DMAX;
     const int i0 = part * IPT;
-    float S[IPT];
+    // key channels i0 .. i0 + IPT of the value channels j0 and j0 + 1; what lies beyond D stays zero
+    float S0[IPT], S1[IPT];
 #pragma unroll
-    for (int ii = 0; ii < IPT; ++ii) S[ii] = (live && i0 + ii < D) ? Sg[(size_t)(i0 + ii) * D + j] : 0.f;
+    for (int ii = 0; ii < IPT; ++ii) {
+        S0[ii] = Sg[(size_t)(2 * ii) * NT + tid];
+        S1[ii] = Sg[(size_t)(2 * ii + 1) * NT + tid];
+    }
     float pre[PRE];
     auto fetch = [&](int tb) {
         const int nt = min(WKV_TOK, t1 - tb);
@@ -319,6 +340,9 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
             pre[x] = (tt < nt && cc < D) ? src[(size_t)(tb + tt) * ld + col + cc] : 0.f;
         }
     };
+    const int warp = tid >> 5, lane = tid & 31;
+    constexpr int n_warps = NT / 32;
+    // the chunk's values into shared memory, then the bonus sums of its tokens, a warp per token
     auto stash = [&]() {
 #pragma unroll
         for (int x = 0; x < PRE; ++x) {
@@ -328,37 +352,58 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
             if (arr == 2) v = cc < D ? expf(-expf(v + w0[col + cc])) : 0.f;
             sm_wkv[e] = v;
         }
+        __syncthreads();
+        for (int tt = warp; tt < WKV_TOK; tt += n_warps) {
+            float c = 0.f;
+            for (int i = lane; i < D; i += 32) c += s_r[tt * DMAX + i] * s_u[i] * s_k[tt * DMAX + i];
+            c = warp_sum(c);
+            if (lane == 0) s_c[tt] = c;
+        }
     };
-    if (t0 < t1) {
-        fetch(t0);
-        stash();
-    }
+    if (t0 < t1) fetch(t0);
+    __syncthreads();                                     // s_u is there
+    if (t0 < t1) stash();
     __syncthreads();
-    const int warp = tid >> 5, lane = tid & 31;
-    constexpr int n_warps = NT / 32;
     for (int tb = t0; tb < t1; tb += WKV_TOK) {
         const int nt = min(WKV_TOK, t1 - tb);
         const bool more = tb + WKV_TOK < t1;
         if (more) fetch(tb + WKV_TOK);
-        for (int tt = 0; tt < nt; ++tt) {
-            const float vj = s_v[tt * DMAX + j];
+        // One token: only S carries over from the token before, so with the loop unrolled the loads and
+        // products of neighbouring tokens overlap.
+        auto token = [&](int tt) {
+            const float2 vj = *reinterpret_cast<const float2*>(s_v + tt * DMAX + j0);
             const float4* r4 = reinterpret_cast<const float4*>(s_r + tt * DMAX + i0);
             const float4* k4 = reinterpret_cast<const float4*>(s_k + tt * DMAX + i0);
             const float4* w4 = reinterpret_cast<const float4*>(s_w + tt * DMAX + i0);
-            const float4* u4 = reinterpret_cast<const float4*>(s_u + i0);
-            float o = 0.f;
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
             for (int q = 0; q < IPT / 4; ++q) {
-                const float4 rr = r4[q], kk = k4[q], ww = w4[q], uu = u4[q];
-                float kv;
-                kv = kk.x * vj; o += rr.x * (S[4 * q] + uu.x * kv); S[4 * q] = ww.x * S[4 * q] + kv;
-                kv = kk.y * vj; o += rr.y * (S[4 * q + 1] + uu.y * kv); S[4 * q + 1] = ww.y * S[4 * q + 1] + kv;
-                kv = kk.z * vj; o += rr.z * (S[4 * q + 2] + uu.z * kv); S[4 * q + 2] = ww.z * S[4 * q + 2] + kv;
-                kv = kk.w * vj; o += rr.w * (S[4 * q + 3] + uu.w * kv); S[4 * q + 3] = ww.w * S[4 * q + 3] + kv;
+                const float4 rr = r4[q], kk = k4[q], ww = w4[q];
+#define WKV_STEP(R, K, W, I, A, B)                                   \
+                A += R * S0[I]; B += R * S1[I];                      \
+                S0[I] = W * S0[I] + K * vj.x; S1[I] = W * S1[I] + K * vj.y;
+                WKV_STEP(rr.x, kk.x, ww.x, 4 * q, a0, b0)
+                WKV_STEP(rr.y, kk.y, ww.y, 4 * q + 1, a1, b1)
+                WKV_STEP(rr.z, kk.z, ww.z, 4 * q + 2, a0, b0)
+                WKV_STEP(rr.w, kk.w, ww.w, 4 * q + 3, a1, b1)
+#undef WKV_STEP
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (part == 0) s_o[tt * DMAX + j] = o;
+            float oa = a0 + a1, ob = b0 + b1;
+#pragma unroll
+            for (int m = 1; m < WKV_PARTS; m <<= 1) {
+                oa += __shfl_xor_sync(0xffffffffu, oa, m);
+                ob += __shfl_xor_sync(0xffffffffu, ob, m);
+            }
+            if (part == 0) {
+                const float c = s_c[tt];
+                *reinterpret_cast<float2*>(s_o + tt * DMAX + j0) = make_float2(oa + c * vj.x, ob + c * vj.y);
+            }
+        };
+        if (nt == WKV_TOK) {
+#pragma unroll 2
+            for (int tt = 0; tt < WKV_TOK; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < nt; ++tt) token(tt);
         }
         __syncthreads();
         for (int tt = warp; tt < nt; tt += n_warps) {
@@ -373,10 +418,10 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
         if (more) stash();
         __syncthreads();
     }
-    if (live) {
 #pragma unroll
-        for (int ii = 0; ii < IPT; ++ii)
-            if (i0 + ii < D) Sg[(size_t)(i0 + ii) * D + j] = S[ii];
+    for (int ii = 0; ii < IPT; ++ii) {
+        Sg[(size_t)(2 * ii) * NT + tid] = S0[ii];
+        Sg[(size_t)(2 * ii + 1) * NT + tid] = S1[ii];
     }
     if (head == 0 && t1 > t0) {
         float* pv = st + prev_off;
@@ -397,7 +442,7 @@ static int launch_wkv(dim3 grid, size_t smem, cudaStream_t stream, const float* 
             raised = true;
         }
     }
-    return rllm_launch(wkv_kernel<TA, DMAX>, grid, dim3(WKV_PARTS * DMAX), smem, stream, rp, kp, vp, wraw, gp, ld, w0, u,
+    return rllm_launch(wkv_kernel<TA, DMAX>, grid, dim3(WKV_PARTS * DMAX / WKV_COLS), smem, stream, rp, kp, vp, wraw, gp, ld, w0, u,
                        norm_w, eps, state, slot_stride, prev_off, (const TA*)h, width, cu_q, slots, (TA*)out, H, D);
 }
 
@@ -410,7 +455,8 @@ RLLM_API int rllm_wkv(const float* rp, const float* kp, const float* vp, const f
     if (D <= 0 || D > 256 || H <= 0) return (int)cudaErrorInvalidValue;
     const dim3 grid(H, n_requests);
     const int dmax = D <= 32 ? 32 : D <= 64 ? 64 : D <= 128 ? 128 : 256;
-    const size_t smem = (size_t)(6 * WKV_TOK + 1) * dmax * sizeof(float);
+    if (prev_off < (long long)H * dmax * dmax) return (int)cudaErrorInvalidValue;
+    const size_t smem = ((size_t)(6 * WKV_TOK + 1) * dmax + WKV_TOK) * sizeof(float);
 #define LAUNCH(TA, DMAX)                                                                                        \
     return launch_wkv<TA, DMAX>(grid, smem, stream, rp, kp, vp, wraw, gp, ld, w0, u, norm_w, eps, state, slot_stride, \
                                 prev_off, h, width, cu_q, slots, out, H, D)
@@ -425,6 +471,12 @@ RLLM_API int rllm_wkv(const float* rp, const float* kp, const float* vp, const f
     BY_D(bf16);
 #undef BY_D
 #undef LAUNCH
+}
+
+// Floats of a request's WKV state for H heads of size D (what precedes the kept previous row in the slot).
+RLLM_API long long rllm_wkv_state_floats(int H, int D) {
+    const int dmax = D <= 32 ? 32 : D <= 64 ? 64 : D <= 128 ? 128 : 256;
+    return (long long)H * dmax * dmax;
 }
 
 RLLM_PACKED(rllm_conv_silu)

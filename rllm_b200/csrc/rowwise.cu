@@ -99,7 +99,7 @@ RLLM_API int rllm_cat2_cast(const float* x, const void* delta, int delta_dt, flo
 // (layouts [page][kv_head][bs][dk] and [page][kv_head][bs][dv]); slot < 0 writes nothing, a slot
 // beyond the pool sets the error word.
 template <typename TI, typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 qkv_rownorm_store_kernel(const TI* qkv, const float* __restrict__ bias, const float* __restrict__ q_norm_w,
                          const float* __restrict__ k_norm_w, const int* __restrict__ slots, TO* q_out, TO* k_cache,
                          TO* v_cache, long long ld, int wq, int wk, int wv, int G, int dk, int dv, int bs, float eps,
@@ -154,8 +154,10 @@ RLLM_API int rllm_qkv_rownorm_store(const void* qkv, int in_dt, long long ld, co
     if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || bs <= 0 || ld < (long long)H * dk + (long long)G * (dk + dv))
         return (int)cudaErrorInvalidValue;
     const int ns = (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots);
+    // a block per token: few tokens (a decode step) get more threads each, since the row's sums keep it in one block
+    const int threads = n < 128 ? 1024 : 256;
 #define LAUNCH(TI, TO)                                                                                         \
-    return rllm_launch(qkv_rownorm_store_kernel<TI, TO>, dim3(n), dim3(256), 0, stream, (const TI*)qkv, bias,  \
+    return rllm_launch(qkv_rownorm_store_kernel<TI, TO>, dim3(n), dim3(threads), 0, stream, (const TI*)qkv, bias,  \
                        q_norm_w, k_norm_w, slots, (TO*)q_out, (TO*)k_cache, (TO*)v_cache, ld, H * dk, G * dk, G * dv, \
                        G, dk, dv, bs, eps, write_kv, ns, err)
     if (in_dt == RLLM_F32 && out_dt == RLLM_F32) { LAUNCH(float, float); }

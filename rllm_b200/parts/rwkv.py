@@ -11,7 +11,8 @@ the first token), H heads of size D:
         S  <- diag(w_t) S + k_t v_t^T
     out  = ((o / rms(o) per head, eps inside the root) * norm * gate) Wo^T
 
-State per request (float32): S of every head and the last row of h, kept from step to step.
+State per request (float32): S of every head (in the WKV kernel's own order, padded to its tile)
+and the last row of h, kept from step to step.
 Parameters: hidden_size, num_heads, head_dim, eps.  Tensors under <prefix>: mu.r, mu.k, mu.v,
 mu.g, mu.w [d]; r, k, v, g [H*D, d]; w1 [low, d], w2 [H*D, low] (low = decay_rank, or what the file has), w0 [H*D]; u [H, D]; norm [H*D];
 o [d, H*D].  The decay, its exponentials, the gate, the unit norm and the state are float32.
@@ -39,7 +40,7 @@ class RWKVTimeMix(Mixer):
         self.eps = float(params.get("eps", 1e-6))
         if self.D > 256:
             raise PartError("rwkv_time_mix: head sizes up to 256")
-        self.prev_off = self.H * self.D * self.D
+        self.prev_off = ops.wkv_state_floats(self.H, self.D)      # the heads' states first, then the previous row
 
     def cache_need(self):
         return StateNeed((self.prev_off + self.hidden_size,), torch.float32)
