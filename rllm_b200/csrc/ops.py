@@ -469,7 +469,7 @@ def conv_silu(xz, weight, bias, state, conv_off, ctx_seq_ids, cu_q, slots, out, 
 
 
 def selective_scan(x, xz, low, b_off, c_off, dtr, dt_bias, A, D, state, conv_off, cu_q, slots, out, n_requests,
-                   inner, N, taps):
+                   inner, N, taps, segments=None):
     """The selective scan over each request's tokens with its state in state[slot, :inner*N]; see
     recurrent.cu.  x, out: activation type [n, inner]; xz, low, dtr float32."""
     _need_cuda(x, xz, low, dtr, dt_bias, A, D, state, out)
@@ -484,11 +484,21 @@ def selective_scan(x, xz, low, b_off, c_off, dtr, dt_bias, A, D, state, conv_off
     assert conv_off >= inner * N and conv_off + inner * (taps - 1) <= st.shape[1]
     if N > 256:
         raise KernelError(f"state size {N} exceeds the scan kernel's limit of 256")
+    sg = segments                              # TimeSegments of the step, or None (defined below)
+    carry = decay = None
+    if sg is not None:
+        carry = torch.empty((sg.n_items, inner * N), dtype=torch.float32, device=out.device)
+        decay = torch.empty((sg.n_items, inner), dtype=torch.float32, device=out.device)
     _check(_lib("recur").rllm_selective_scan(
         _ptr(x), c_int(_code(x)), _ptr(xz), c_longlong(xz.stride(0)), _ptr(low), c_longlong(low.stride(0)),
         c_int(b_off), c_int(c_off), _ptr(dtr), _ptr(dt_bias), _ptr(A), _ptr(D), _ptr(st), c_longlong(st.stride(0)),
         c_longlong(conv_off), _ptr(cu_q), _ptr(slots), _ptr(out), c_int(n_requests), c_int(inner), c_int(N),
-        c_int(taps), _stream()), "selective_scan")
+        c_int(taps), _ptr(sg.t0 if sg else None), _ptr(sg.t1 if sg else None), _ptr(sg.req if sg else None),
+        _ptr(sg.flags if sg else None), _ptr(sg.item0 if sg else None), _ptr(sg.items if sg else None),
+        c_int(sg.n_items if sg else 0), _ptr(carry), _ptr(decay), _stream()), "selective_scan")
+    if sg is not None:
+        global _launches
+        _launches += 2                         # the local pass and the combine kernel
     return out
 
 
@@ -515,9 +525,52 @@ def wkv_state_floats(H: int, D: int) -> int:
     return H * dmax * dmax
 
 
-def wkv(r, k, v, wraw, g, w0, u, norm_w, eps, state, prev_off, h, cu_q, slots, out, n_requests, H, D):
+SEGMENT_TOKENS = 128      # length of a segment when long portions are cut along time
+SEGMENT_FROM = 256        # shortest portion that is cut
+TIME_SEGMENTS = os.environ.get("RLLM_B200_NO_TIME_SEGMENTS", "0") in ("", "0")
+
+
+class TimeSegments:
+    """The step's requests cut along time for the recurrent kernels (recurrent.cu, TimeSegments): a
+    request that brings fewer than SEGMENT_FROM tokens is one item, a longer one several of
+    SEGMENT_TOKENS tokens (the last takes the remainder).  Built once per step on the host from the
+    step's shape and shared by all layers."""
+
+    def __init__(self, ctx, device):
+        t0, t1, req, flags, item0, items = [], [], [], [], [], []
+        base = 0
+        for r, q in enumerate(ctx.q_lens):
+            n = q // SEGMENT_TOKENS if q >= SEGMENT_FROM else 1
+            item0.append(len(t0))
+            items.append(n)
+            for s in range(n):
+                t0.append(base + s * SEGMENT_TOKENS)
+                t1.append(base + (s + 1) * SEGMENT_TOKENS if s + 1 < n else base + q)
+                req.append(r)
+                flags.append((1 if s == 0 else 0) | (2 if s + 1 == n else 0))
+            base += q
+        self.n_items = len(t0)
+        flat = torch.tensor(t0 + t1 + req + flags + item0 + items, dtype=torch.int32).to(device)
+        n, R = self.n_items, len(items)
+        self.t0, self.t1, self.req, self.flags = flat[:n], flat[n:2 * n], flat[2 * n:3 * n], flat[3 * n:4 * n]
+        self.item0, self.items = flat[4 * n:4 * n + R], flat[4 * n + R:4 * n + 2 * R]
+
+
+def time_segments(ctx, device):
+    """The step's TimeSegments, or None when no request brings a portion long enough to cut."""
+    if not TIME_SEGMENTS or ctx.max_q_len < SEGMENT_FROM:
+        return None
+    plan = ctx.plans.get("time_segments")
+    if plan is None:
+        plan = ctx.plans["time_segments"] = TimeSegments(ctx, device)
+    return plan
+
+
+def wkv(r, k, v, wraw, g, w0, u, norm_w, eps, state, prev_off, h, cu_q, slots, out, n_requests, H, D, segments=None):
     """The RWKV recurrence with data-dependent decay, unit norm per head, norm weight and silu gate; see
-    recurrent.cu.  r, k, v, wraw, g float32 [n, H*D] (equal row strides); out activation type."""
+    recurrent.cu.  r, k, v, wraw, g float32 [n, H*D] (equal row strides); out activation type.
+    segments: the step's TimeSegments (long portions are then worked through segment by segment, side
+    by side) or None."""
     _need_cuda(r, k, v, wraw, g, w0, u, norm_w, state, h, out)
     n = out.shape[0]
     for name, t in (("r", r), ("k", k), ("v", v), ("wraw", wraw), ("g", g)):
@@ -531,10 +584,23 @@ def wkv(r, k, v, wraw, g, w0, u, norm_w, eps, state, prev_off, h, cu_q, slots, o
         raise KernelError(f"head size {D} exceeds the WKV kernel's limit of 256")
     st = _state2d(state)
     assert prev_off >= wkv_state_floats(H, D) and prev_off + h.shape[1] <= st.shape[1]
+    sg = segments
+    carry = decay = None
+    if sg is not None:
+        per_head = wkv_state_floats(1, D)
+        carry = torch.empty((sg.n_items, H, per_head), dtype=torch.float32, device=out.device)
+        decay = torch.empty((sg.n_items, H, int(per_head ** 0.5)), dtype=torch.float32, device=out.device)
     _check(_lib("recur").rllm_wkv(_ptr(r), _ptr(k), _ptr(v), _ptr(wraw), _ptr(g), c_longlong(r.stride(0)), _ptr(w0),
                                   _ptr(u), _ptr(norm_w), c_float(eps), _ptr(st), c_longlong(st.stride(0)),
                                   c_longlong(prev_off), _ptr(h), c_int(_code(h)), c_int(h.shape[1]), _ptr(cu_q),
-                                  _ptr(slots), _ptr(out), c_int(n_requests), c_int(H), c_int(D), _stream()), "wkv")
+                                  _ptr(slots), _ptr(out), c_int(n_requests), c_int(H), c_int(D),
+                                  _ptr(sg.t0 if sg else None), _ptr(sg.t1 if sg else None), _ptr(sg.req if sg else None),
+                                  _ptr(sg.flags if sg else None), _ptr(sg.item0 if sg else None),
+                                  _ptr(sg.items if sg else None), c_int(sg.n_items if sg else 0), _ptr(carry),
+                                  _ptr(decay), _stream()), "wkv")
+    if sg is not None:
+        global _launches
+        _launches += 2                         # the local pass and the combine kernel
     return out
 
 

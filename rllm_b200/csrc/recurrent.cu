@@ -74,18 +74,35 @@ RLLM_API int rllm_conv_silu(const float* xz, long long ld, const float* w, const
 // C of a chunk lie in shared memory, and the next chunk's values are already on their way from global
 // memory (held in registers) while this one is worked through, so the recurrence never waits for a
 // load.  At the end the convolution's kept inputs move on by this step's tokens.
+// Long portions are also cut along time, as for the WKV kernel below (TimeSegments): a segment
+// multiplies the state by exp(A * sum of its step sizes) and adds its end state from a zero start.
+// PASS 0: whole requests.  1: the local end state and the sum of the step sizes, no output.  2: from
+// the carried start state, with output.
+// Segments of the step's requests along time; all null / zero: every request is one item.
+struct TimeSegments {
+    const int* t0;        // [items] first flat token
+    const int* t1;        // [items] one past the last
+    const int* req;       // [items] the request's row in the step
+    const int* flags;     // [items] bit 0: first segment of its request, bit 1: last
+    const int* req_item0; // [requests] a request's first item
+    const int* req_items; // [requests] how many it has
+    float* carry;         // [items][rows of state per item]: local end states, then true end states
+    float* decay;         // [items][...]: what the combine step multiplies the start state by
+    int n_items;
+};
+
 #define SCAN_LANES 4
 #define SCAN_CH 32            // channels per block (128 threads)
 #define SCAN_TOK 16           // tokens per chunk
 #define SCAN_THREADS (SCAN_LANES * SCAN_CH)
 
-template <typename TA, int NPT>
+template <typename TA, int NPT, int PASS>
 __global__ void __launch_bounds__(SCAN_THREADS)
 selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float* low, long long ld_low, int b_off,
                       int c_off, const float* dtr, const float* __restrict__ dt_b, const float* __restrict__ A,
                       const float* __restrict__ Dp, float* state, long long slot_stride, long long conv_off,
                       const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int inner, int N,
-                      int taps) {
+                      int taps, const TimeSegments seg) {
     constexpr int PRE_X = 3 * SCAN_TOK * SCAN_CH / SCAN_THREADS;      // x, dt, z of a chunk: values per thread
     constexpr int PRE_BC = NPT;                                        // B and C of a chunk (N <= SCAN_LANES * NPT)
     extern __shared__ float sm_scan[];
@@ -95,20 +112,28 @@ selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float
     float* s_bc = s_z + SCAN_TOK * SCAN_CH;              // [SCAN_TOK][2][N]
     pdl_wait();
     pdl_launch_dependents();
-    const int r = blockIdx.y;
-    const int t0 = cu_q[r], t1 = cu_q[r + 1];
+    const int item = blockIdx.y;
+    const int r = PASS == 0 ? item : seg.req[item];
+    const int t0 = PASS == 0 ? cu_q[r] : seg.t0[item], t1 = PASS == 0 ? cu_q[r + 1] : seg.t1[item];
+    const bool first = PASS == 0 || (seg.flags[item] & 1), last = PASS == 0 || (seg.flags[item] & 2);
+    if (PASS == 1 && last) return;                       // its end state comes out of pass 2
     const int tid = threadIdx.x, lane = tid % SCAN_LANES, cl = tid / SCAN_LANES;
     const int c_base = blockIdx.x * SCAN_CH;
     const int c_own = c_base + cl;
     const bool live = c_own < inner;
     const int c = live ? c_own : inner - 1;             // lanes beyond the last channel shadow it and write nothing
     float* st = state + (size_t)slots[r] * slot_stride;
+    // the start state: the slot; with several segments the combine step's copy of it or the end state of the
+    // segment before (the last segment overwrites the slot while the first may not have started)
+    const int src = first ? item + (PASS == 0 ? 0 : seg.req_items[r]) - 1 : item - 1;
+    const float* from = (first && last) ? st : seg.carry + (size_t)src * inner * N;
     float S[NPT], a[NPT];
+    float sum_dt = 0.f;
 #pragma unroll
     for (int k = 0; k < NPT; ++k) {
         const int n = lane + SCAN_LANES * k;
         const bool on = n < N;
-        S[k] = on ? st[(size_t)c * N + n] : 0.f;
+        S[k] = (on && PASS != 1) ? from[(size_t)c * N + n] : 0.f;
         a[k] = on ? A[(size_t)c * N + n] : 0.f;
     }
     const float dd = Dp[c];
@@ -170,14 +195,16 @@ selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float
             const float* Bt = s_bc + tt * 2 * N;
             const float* Ct = Bt + N;
             float part = 0.f;
+            if (PASS == 1) sum_dt += dt;
 #pragma unroll
             for (int k = 0; k < NPT; ++k) {
                 const int n = lane + SCAN_LANES * k;
                 if (n < N) {
                     S[k] = expf(dt * a[k]) * S[k] + dx * Bt[n];
-                    part += S[k] * Ct[n];
+                    if (PASS != 1) part += S[k] * Ct[n];
                 }
             }
+            if (PASS == 1) return;
             part += __shfl_xor_sync(0xffffffffu, part, 1);
             part += __shfl_xor_sync(0xffffffffu, part, 2);
             if (lane == 0 && live)
@@ -194,6 +221,17 @@ selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float
         __syncthreads();
     }
     if (!live) return;
+    if (PASS == 1) {
+        float* to = seg.carry + (size_t)item * inner * N;
+#pragma unroll
+        for (int k = 0; k < NPT; ++k) {
+            const int n = lane + SCAN_LANES * k;
+            if (n < N) to[(size_t)c * N + n] = S[k];
+        }
+        if (lane == 0) seg.decay[(size_t)item * inner + c] = sum_dt;
+        return;
+    }
+    if (!last) return;
 #pragma unroll
     for (int k = 0; k < NPT; ++k) {
         const int n = lane + SCAN_LANES * k;
@@ -202,27 +240,89 @@ selective_scan_kernel(const TA* x, const float* xz, long long ld_xz, const float
     if (lane == 0 && taps > 1) {
         // kept inputs: the last taps-1 of (old kept inputs ++ this step's inputs), oldest first
         float* cs = st + conv_off + (size_t)c * (taps - 1);
-        const int q = t1 - t0;
+        const int q0 = cu_q[r], q = t1 - q0;             // the request's tokens of this step, all segments
         for (int k = 0; k < taps - 1; ++k) {
             const int idx = q + k;                       // place in the joined sequence
-            cs[k] = idx < taps - 1 ? cs[idx] : xz[(size_t)(t0 + idx - (taps - 1)) * ld_xz + c];
+            cs[k] = idx < taps - 1 ? cs[idx] : xz[(size_t)(q0 + idx - (taps - 1)) * ld_xz + c];
         }
     }
 }
 
+// Between the passes: a request's segments in order, S_end = exp(A * sum of step sizes) * S_start + local
+// end state, in place; the start state is copied to where the last segment's local state would be.
+template <int NPT>
+__global__ void __launch_bounds__(SCAN_THREADS)
+scan_combine_kernel(const float* state, long long slot_stride, const int* __restrict__ slots,
+                    const float* __restrict__ A, int inner, int N, const TimeSegments seg) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.y;
+    const int n_it = seg.req_items[r], item0 = seg.req_item0[r];
+    if (n_it < 2) return;
+    const int tid = threadIdx.x, lane = tid % SCAN_LANES;
+    const int c = blockIdx.x * SCAN_CH + tid / SCAN_LANES;
+    if (c >= inner) return;
+    const float* st = state + (size_t)slots[r] * slot_stride;
+    float S[NPT], a[NPT];
+    float* keep = seg.carry + (size_t)(item0 + n_it - 1) * inner * N;
+#pragma unroll
+    for (int k = 0; k < NPT; ++k) {
+        const int n = lane + SCAN_LANES * k;
+        S[k] = n < N ? st[(size_t)c * N + n] : 0.f;
+        a[k] = n < N ? A[(size_t)c * N + n] : 0.f;
+        if (n < N) keep[(size_t)c * N + n] = S[k];
+    }
+    for (int it = item0; it < item0 + n_it - 1; ++it) {
+        float* C = seg.carry + (size_t)it * inner * N;
+        const float sum_dt = seg.decay[(size_t)it * inner + c];
+#pragma unroll
+        for (int k = 0; k < NPT; ++k) {
+            const int n = lane + SCAN_LANES * k;
+            if (n < N) {
+                S[k] = expf(sum_dt * a[k]) * S[k] + C[(size_t)c * N + n];
+                C[(size_t)c * N + n] = S[k];
+            }
+        }
+    }
+}
+
+template <typename TA, int NPT>
+static int launch_scan(int n_requests, size_t smem, cudaStream_t stream, const void* x, const float* xz, long long ld_xz,
+                       const float* low, long long ld_low, int b_off, int c_off, const float* dtr, const float* dt_b,
+                       const float* A, const float* Dp, float* state, long long slot_stride, long long conv_off,
+                       const int* cu_q, const int* slots, void* out, int inner, int N, int taps, const TimeSegments& seg) {
+    const int cols = (inner + SCAN_CH - 1) / SCAN_CH;
+#define SCAN_ARGS (const TA*)x, xz, ld_xz, low, ld_low, b_off, c_off, dtr, dt_b, A, Dp, state, slot_stride, conv_off, cu_q, \
+                  slots, (TA*)out, inner, N, taps, seg
+    if (seg.n_items <= 0)
+        return rllm_launch(selective_scan_kernel<TA, NPT, 0>, dim3(cols, n_requests), dim3(SCAN_THREADS), smem, stream, SCAN_ARGS);
+    int st = rllm_launch(selective_scan_kernel<TA, NPT, 1>, dim3(cols, seg.n_items), dim3(SCAN_THREADS), smem, stream, SCAN_ARGS);
+    if (st) return st;
+    st = rllm_launch(scan_combine_kernel<NPT>, dim3(cols, n_requests), dim3(SCAN_THREADS), 0, stream, (const float*)state,
+                     slot_stride, slots, A, inner, N, seg);
+    if (st) return st;
+    return rllm_launch(selective_scan_kernel<TA, NPT, 2>, dim3(cols, seg.n_items), dim3(SCAN_THREADS), smem, stream, SCAN_ARGS);
+#undef SCAN_ARGS
+}
+
+// seg_* / carry / decay: the cut along time (TimeSegments; n_items 0: none).  carry needs n_items * inner * N
+// floats, decay n_items * inner.
 RLLM_API int rllm_selective_scan(const void* x, int act_dt, const float* xz, long long ld_xz, const float* low,
                                  long long ld_low, int b_off, int c_off, const float* dtr, const float* dt_b,
                                  const float* A, const float* Dp, float* state, long long slot_stride,
                                  long long conv_off, const int* cu_q, const int* slots, void* out, int n_requests,
-                                 int inner, int N, int taps, cudaStream_t stream) {
+                                 int inner, int N, int taps, const int* seg_t0, const int* seg_t1, const int* seg_req,
+                                 const int* seg_flags, const int* req_item0, const int* req_items, int n_items,
+                                 float* carry, float* decay, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (N <= 0 || N > SCAN_LANES * 64 || inner <= 0 || taps < 1) return (int)cudaErrorInvalidValue;
-    const dim3 grid((inner + SCAN_CH - 1) / SCAN_CH, n_requests), block(SCAN_THREADS);
+    TimeSegments seg = {seg_t0, seg_t1, seg_req, seg_flags, req_item0, req_items, carry, decay, n_items};
+    if (n_items > 0 && (!seg_t0 || !seg_t1 || !seg_req || !seg_flags || !req_item0 || !req_items || !carry || !decay))
+        return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(3 * SCAN_TOK * SCAN_CH + SCAN_TOK * 2 * N) * sizeof(float);
 #define LAUNCH(TA, NPT)                                                                                          \
-    return rllm_launch(selective_scan_kernel<TA, NPT>, grid, block, smem, stream, (const TA*)x, xz, ld_xz, low,  \
-                       ld_low, b_off, c_off, dtr, dt_b, A, Dp, state, slot_stride, conv_off, cu_q, slots, (TA*)out, \
-                       inner, N, taps)
+    return launch_scan<TA, NPT>(n_requests, smem, stream, x, xz, ld_xz, low, ld_low, b_off, c_off, dtr, dt_b, A, Dp, \
+                                state, slot_stride, conv_off, cu_q, slots, out, inner, N, taps, seg)
 #define BY_N(TA)                                                                                                 \
     do {                                                                                                         \
         if (N <= SCAN_LANES * 4) { LAUNCH(TA, 4); }                                                              \
@@ -289,16 +389,28 @@ RLLM_API int rllm_token_shift(const void* h, int act_dt, const float* mu, const 
 // time), the next chunk's values are already on their way from global memory (held in registers)
 // while this one is worked through, and the chunk's outputs are normalised by the warps in turn.
 // The kept previous row moves on at the end.
+//
+// Long portions are also cut along time (TimeSegments): the decay is diagonal, so a segment's effect on
+// the state is  S_end = diag(prod of its decays) S_start + (its end state from a zero start).  Pass 1
+// works out the second term and the product for every segment but a request's last, all segments side
+// by side; a small kernel then walks each request's segments and turns the local end states into true
+// ones; pass 2 runs every segment from its true start state and writes the outputs (the last one also
+// the request's state).  Twice the arithmetic, as many blocks as segments x heads.  The sums inside a
+// segment run in the same order as without the cut; across the cut they are associated differently,
+// which moves results by rounding only.
 #define WKV_TOK 16
 #define WKV_PARTS 8
 #define WKV_COLS 2
 
-template <typename TA, int DMAX>
+// PASS 0: whole requests.  1: end state from a zero start and the product of the decays, no output.
+// 2: from the carried start state, with output.
+template <typename TA, int DMAX, int PASS>
 __global__ void __launch_bounds__(WKV_PARTS * DMAX / WKV_COLS)
 wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw, const float* gp, long long ld,
            const float* __restrict__ w0, const float* __restrict__ u, const float* __restrict__ norm_w, float eps,
            float* state, long long slot_stride, long long prev_off, const TA* h, int width,
-           const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int H, int D) {
+           const int* __restrict__ cu_q, const int* __restrict__ slots, TA* out, int H, int D,
+           const TimeSegments seg) {
     constexpr int IPT = DMAX / WKV_PARTS;               // key channels per thread
     constexpr int NT = WKV_PARTS * DMAX / WKV_COLS;     // threads
     constexpr int TD = WKV_TOK * DMAX;
@@ -313,21 +425,32 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
     float* s_u = s_o + TD;
     float* s_c = s_u + DMAX;
     const int tid = threadIdx.x, j0 = WKV_COLS * (tid / WKV_PARTS), part = tid % WKV_PARTS;
-    const int head = blockIdx.x, r = blockIdx.y;
+    const int head = blockIdx.x, item = blockIdx.y;
     const size_t col = (size_t)head * D;
     for (int i = tid; i < DMAX; i += NT) s_u[i] = i < D ? u[col + i] : 0.f;
     pdl_wait();
     pdl_launch_dependents();
-    const int t0 = cu_q[r], t1 = cu_q[r + 1];
+    const int r = PASS == 0 ? item : seg.req[item];
+    const int t0 = PASS == 0 ? cu_q[r] : seg.t0[item], t1 = PASS == 0 ? cu_q[r + 1] : seg.t1[item];
+    const bool first = PASS == 0 || (seg.flags[item] & 1), last = PASS == 0 || (seg.flags[item] & 2);
+    if (PASS == 1 && last) return;                       // its end state comes out of pass 2
     float* st = state + (size_t)slots[r] * slot_stride;
     float* Sg = st + (size_t)head * DMAX * DMAX;
     const int i0 = part * IPT;
     // key channels i0 .. i0 + IPT of the value channels j0 and j0 + 1; what lies beyond D stays zero
-    float S0[IPT], S1[IPT];
+    float S0[IPT], S1[IPT], cw[PASS == 1 ? IPT : 1];
+    {
+        // A request's start state: in its slot; with several segments the combine step has put a copy
+        // where the last segment's local state would be, because the last segment overwrites the slot
+        // while the first may not have started.
+        const int src = first ? item + seg.req_items[r] - 1 : item - 1;
+        const float* from = (first && last) ? Sg : seg.carry + ((size_t)src * H + head) * DMAX * DMAX;
 #pragma unroll
-    for (int ii = 0; ii < IPT; ++ii) {
-        S0[ii] = Sg[(size_t)(2 * ii) * NT + tid];
-        S1[ii] = Sg[(size_t)(2 * ii + 1) * NT + tid];
+        for (int ii = 0; ii < IPT; ++ii) {
+            S0[ii] = PASS == 1 ? 0.f : from[(size_t)(2 * ii) * NT + tid];
+            S1[ii] = PASS == 1 ? 0.f : from[(size_t)(2 * ii + 1) * NT + tid];
+            if (PASS == 1) cw[ii] = 1.f;
+        }
     }
     float pre[PRE];
     auto fetch = [&](int tb) {
@@ -380,7 +503,8 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
             for (int q = 0; q < IPT / 4; ++q) {
                 const float4 rr = r4[q], kk = k4[q], ww = w4[q];
 #define WKV_STEP(R, K, W, I, A, B)                                   \
-                A += R * S0[I]; B += R * S1[I];                      \
+                if (PASS != 1) { A += R * S0[I]; B += R * S1[I]; }   \
+                else cw[I] *= W;                                     \
                 S0[I] = W * S0[I] + K * vj.x; S1[I] = W * S1[I] + K * vj.y;
                 WKV_STEP(rr.x, kk.x, ww.x, 4 * q, a0, b0)
                 WKV_STEP(rr.y, kk.y, ww.y, 4 * q + 1, a1, b1)
@@ -388,6 +512,7 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
                 WKV_STEP(rr.w, kk.w, ww.w, 4 * q + 3, a1, b1)
 #undef WKV_STEP
             }
+            if (PASS == 1) return;
             float oa = a0 + a1, ob = b0 + b1;
 #pragma unroll
             for (int m = 1; m < WKV_PARTS; m <<= 1) {
@@ -406,7 +531,7 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
             for (int tt = 0; tt < nt; ++tt) token(tt);
         }
         __syncthreads();
-        for (int tt = warp; tt < nt; tt += n_warps) {
+        for (int tt = warp; PASS != 1 && tt < nt; tt += n_warps) {
             float ss = 0.f;
             for (int i = lane; i < D; i += 32) ss += s_o[tt * DMAX + i] * s_o[tt * DMAX + i];
             const float rs = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
@@ -418,6 +543,17 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
         if (more) stash();
         __syncthreads();
     }
+    if (PASS == 1) {
+        float* to = seg.carry + ((size_t)item * H + head) * DMAX * DMAX;
+#pragma unroll
+        for (int ii = 0; ii < IPT; ++ii) {
+            to[(size_t)(2 * ii) * NT + tid] = S0[ii];
+            to[(size_t)(2 * ii + 1) * NT + tid] = S1[ii];
+            if (tid < WKV_PARTS) seg.decay[((size_t)item * H + head) * DMAX + i0 + ii] = cw[ii];
+        }
+        return;
+    }
+    if (!last) return;
 #pragma unroll
     for (int ii = 0; ii < IPT; ++ii) {
         Sg[(size_t)(2 * ii) * NT + tid] = S0[ii];
@@ -429,37 +565,105 @@ wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw,
     }
 }
 
-template <typename TA, int DMAX>
-static int launch_wkv(dim3 grid, size_t smem, cudaStream_t stream, const float* rp, const float* kp, const float* vp,
-                      const float* wraw, const float* gp, long long ld, const float* w0, const float* u,
-                      const float* norm_w, float eps, float* state, long long slot_stride, long long prev_off,
-                      const void* h, int width, const int* cu_q, const int* slots, void* out, int H, int D) {
+// Between the passes: a request's segments in order, S_end = decay * S_start + local end state, in place.
+template <int DMAX>
+__global__ void __launch_bounds__(WKV_PARTS * DMAX / WKV_COLS)
+wkv_combine_kernel(const float* state, long long slot_stride, const int* __restrict__ slots, int H, const TimeSegments seg) {
+    constexpr int IPT = DMAX / WKV_PARTS;
+    constexpr int NT = WKV_PARTS * DMAX / WKV_COLS;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, head = blockIdx.x, r = blockIdx.y;
+    const int n = seg.req_items[r], item0 = seg.req_item0[r];
+    if (n < 2) return;
+    const float* Sg = state + (size_t)slots[r] * slot_stride + (size_t)head * DMAX * DMAX;
+    const int i0 = (tid % WKV_PARTS) * IPT;
+    float S0[IPT], S1[IPT];
+#pragma unroll
+    for (int ii = 0; ii < IPT; ++ii) {
+        S0[ii] = Sg[(size_t)(2 * ii) * NT + tid];
+        S1[ii] = Sg[(size_t)(2 * ii + 1) * NT + tid];
+    }
+    {
+        float* keep = seg.carry + ((size_t)(item0 + n - 1) * H + head) * DMAX * DMAX;    // the start state, for pass 2
+#pragma unroll
+        for (int ii = 0; ii < IPT; ++ii) {
+            keep[(size_t)(2 * ii) * NT + tid] = S0[ii];
+            keep[(size_t)(2 * ii + 1) * NT + tid] = S1[ii];
+        }
+    }
+    for (int it = item0; it < item0 + n - 1; ++it) {
+        float* C = seg.carry + ((size_t)it * H + head) * DMAX * DMAX;
+        const float* dec = seg.decay + ((size_t)it * H + head) * DMAX + i0;
+#pragma unroll
+        for (int ii = 0; ii < IPT; ++ii) {
+            const float w = dec[ii];
+            S0[ii] = w * S0[ii] + C[(size_t)(2 * ii) * NT + tid];
+            S1[ii] = w * S1[ii] + C[(size_t)(2 * ii + 1) * NT + tid];
+            C[(size_t)(2 * ii) * NT + tid] = S0[ii];
+            C[(size_t)(2 * ii + 1) * NT + tid] = S1[ii];
+        }
+    }
+}
+
+template <typename TA, int DMAX, int PASS>
+static int launch_wkv_pass(dim3 grid, size_t smem, cudaStream_t stream, const float* rp, const float* kp,
+                           const float* vp, const float* wraw, const float* gp, long long ld, const float* w0,
+                           const float* u, const float* norm_w, float eps, float* state, long long slot_stride,
+                           long long prev_off, const void* h, int width, const int* cu_q, const int* slots, void* out,
+                           int H, int D, const TimeSegments& seg) {
     if (smem > 48 * 1024) {
         static bool raised = false;                      // once per instantiation: more dynamic shared memory than the default
         if (!raised) {
-            cudaError_t e = cudaFuncSetAttribute(wkv_kernel<TA, DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = cudaFuncSetAttribute(wkv_kernel<TA, DMAX, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)smem);
             if (e != cudaSuccess) return (int)e;
             raised = true;
         }
     }
-    return rllm_launch(wkv_kernel<TA, DMAX>, grid, dim3(WKV_PARTS * DMAX / WKV_COLS), smem, stream, rp, kp, vp, wraw, gp, ld, w0, u,
-                       norm_w, eps, state, slot_stride, prev_off, (const TA*)h, width, cu_q, slots, (TA*)out, H, D);
+    return rllm_launch(wkv_kernel<TA, DMAX, PASS>, grid, dim3(WKV_PARTS * DMAX / WKV_COLS), smem, stream, rp, kp, vp, wraw,
+                       gp, ld, w0, u, norm_w, eps, state, slot_stride, prev_off, (const TA*)h, width, cu_q, slots, (TA*)out,
+                       H, D, seg);
 }
 
+template <typename TA, int DMAX>
+static int launch_wkv(int n_requests, size_t smem, cudaStream_t stream, const float* rp, const float* kp, const float* vp,
+                      const float* wraw, const float* gp, long long ld, const float* w0, const float* u,
+                      const float* norm_w, float eps, float* state, long long slot_stride, long long prev_off,
+                      const void* h, int width, const int* cu_q, const int* slots, void* out, int H, int D,
+                      const TimeSegments& seg) {
+#define WKV_ARGS rp, kp, vp, wraw, gp, ld, w0, u, norm_w, eps, state, slot_stride, prev_off, h, width, cu_q, slots, out, H, D, seg
+    if (seg.n_items <= 0)
+        return launch_wkv_pass<TA, DMAX, 0>(dim3(H, n_requests), smem, stream, WKV_ARGS);
+    int st = launch_wkv_pass<TA, DMAX, 1>(dim3(H, seg.n_items), smem, stream, WKV_ARGS);
+    if (st) return st;
+    st = rllm_launch(wkv_combine_kernel<DMAX>, dim3(H, n_requests), dim3(WKV_PARTS * DMAX / WKV_COLS), 0, stream,
+                     (const float*)state, slot_stride, slots, H, seg);
+    if (st) return st;
+    return launch_wkv_pass<TA, DMAX, 2>(dim3(H, seg.n_items), smem, stream, WKV_ARGS);
+#undef WKV_ARGS
+}
+
+// seg_* / carry / decay: the cut along time (TimeSegments; n_items 0: none).  carry needs n_items * H * DMAX * DMAX
+// floats, decay n_items * H * DMAX (DMAX as in rllm_wkv_state_floats).
 RLLM_API int rllm_wkv(const float* rp, const float* kp, const float* vp, const float* wraw, const float* gp,
                       long long ld, const float* w0, const float* u, const float* norm_w, float eps, float* state,
                       long long slot_stride, long long prev_off, const void* h, int act_dt, int width,
                       const int* cu_q, const int* slots, void* out, int n_requests, int H, int D,
+                      const int* seg_t0, const int* seg_t1, const int* seg_req, const int* seg_flags,
+                      const int* req_item0, const int* req_items, int n_items, float* carry, float* decay,
                       cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (D <= 0 || D > 256 || H <= 0) return (int)cudaErrorInvalidValue;
-    const dim3 grid(H, n_requests);
     const int dmax = D <= 32 ? 32 : D <= 64 ? 64 : D <= 128 ? 128 : 256;
     if (prev_off < (long long)H * dmax * dmax) return (int)cudaErrorInvalidValue;
+    TimeSegments seg = {seg_t0, seg_t1, seg_req, seg_flags, req_item0, req_items, carry, decay, n_items};
+    if (n_items > 0 && (!seg_t0 || !seg_t1 || !seg_req || !seg_flags || !req_item0 || !req_items || !carry || !decay))
+        return (int)cudaErrorInvalidValue;
     const size_t smem = ((size_t)(6 * WKV_TOK + 1) * dmax + WKV_TOK) * sizeof(float);
 #define LAUNCH(TA, DMAX)                                                                                        \
-    return launch_wkv<TA, DMAX>(grid, smem, stream, rp, kp, vp, wraw, gp, ld, w0, u, norm_w, eps, state, slot_stride, \
-                                prev_off, h, width, cu_q, slots, out, H, D)
+    return launch_wkv<TA, DMAX>(n_requests, smem, stream, rp, kp, vp, wraw, gp, ld, w0, u, norm_w, eps, state,  \
+                                slot_stride, prev_off, h, width, cu_q, slots, out, H, D, seg)
 #define BY_D(TA)                                                                                               \
     do {                                                                                                       \
         if (dmax == 32) { LAUNCH(TA, 32); }                                                                    \

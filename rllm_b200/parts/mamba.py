@@ -70,5 +70,6 @@ class Mamba1(Mixer):
         dtr = ops.linear(step_in, self.w_dt, out_dtype=torch.float32)
         y = torch.empty((n, I), dtype=dt, device=dev)
         ops.selective_scan(x, xz, low, R, R + N, dtr, self.dt_b, self.A, self.Dp, cache.state, self.conv_off,
-                           ctx.cu_q, cache.slots, y, ctx.n_requests, I, N, self.taps)
+                           ctx.cu_q, cache.slots, y, ctx.n_requests, I, N, self.taps,
+                           segments=ops.time_segments(ctx, dev))
         return ops.linear(y, self.w_o, out_dtype=torch.float32)

@@ -78,5 +78,6 @@ class RWKVTimeMix(Mixer):
         ops.linear(low_t, self.w_2, out=proj[4])
         out = torch.empty((n, HD), dtype=dt, device=dev)
         ops.wkv(proj[0], proj[1], proj[2], proj[4], proj[3], self.w0, self.u.view(-1), self.norm_w, self.eps,
-                cache.state, self.prev_off, h, ctx.cu_q, cache.slots, out, ctx.n_requests, self.H, self.D)
+                cache.state, self.prev_off, h, ctx.cu_q, cache.slots, out, ctx.n_requests, self.H, self.D,
+                segments=ops.time_segments(ctx, dev))
         return ops.linear(out, self.w_o, out_dtype=torch.float32)

@@ -294,6 +294,37 @@ def test_long_prompt_then_long_decoding(dtype):
     compare(out, {"a": ref}, dtype, "long decoding")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["time_mix", "time_mix_one_head", "mamba", "mamba_wide_state", "loop1_tail"])
+def test_long_portions_cut_along_time(name, dtype):
+    """Portions of 256 tokens and more are cut into segments that the recurrent kernels work through
+    side by side (local end states, a combine step, then the outputs).  Requests of 700 and 300 tokens
+    in one step beside one of 5; then the rest of the first in a portion of 257 beside single tokens
+    of the others; then single tokens: every row and the states left behind are the plain ones."""
+    from rllm_b200.csrc import ops
+    cfg = CASES[name]
+    w = fc.make_weights(cfg, 14, stored(dtype))
+    toks = {"a": fc.tokens_for(cfg, 970, 50), "b": fc.tokens_for(cfg, 310, 51), "c": fc.tokens_for(cfg, 15, 52)}
+    refs = {r: fc.oracle(cfg, w, t) for r, t in toks.items()}
+    eng = fc.build_engine(cfg, w, dtype, max_tokens=1400, block_size=16, max_requests=3)
+    made = []
+    real = ops.TimeSegments.__init__
+    ops.TimeSegments.__init__ = lambda self, *a, **k: made.append(1) or real(self, *a, **k)
+    try:
+        sample = lambda lo, hi: sorted(set(range(lo, hi, 37)) | {hi - 1, lo})
+        steps = [([("a", toks["a"][:700], sample(0, 700)), ("b", toks["b"][:300], sample(0, 300)),
+                   ("c", toks["c"][:5], [0, 4])], []),
+                 ([("a", toks["a"][700:957], sample(0, 257)), ("b", [toks["b"][300]], [0]), ("c", [toks["c"][5]], [0])], [])]
+        for i in range(9):
+            steps.append(([("a", [toks["a"][957 + i]], [0]), ("b", [toks["b"][301 + i]], [0]),
+                           ("c", [toks["c"][6 + i]], [0])], []))
+        out = run(eng, steps)
+    finally:
+        ops.TimeSegments.__init__ = real
+    assert len(made) == 2, "the two steps with long portions were not cut"
+    compare(out, refs, dtype, f"{name}, long portions")
+
+
 def test_graph_replay_equals_eager_steps():
     """Decode steps replayed from CUDA graphs (padded to four requests and a context bucket, the
     padding rows on the spare state slot) give what the same steps give launched one by one."""
