@@ -325,6 +325,30 @@ def test_long_portions_cut_along_time(name, dtype):
     compare(out, refs, dtype, f"{name}, long portions")
 
 
+BIG = {
+    # sizes that take the kernels' other instantiations: time-mixing heads of 96, 128 and 200 (tiles of 128 and
+    # 256, more shared memory than the default), 70 and 200 states per channel, attention heads of 192 / 320
+    "heads_96_128": fc.config([fc.parallel(fc.att(2, 1, 192, 320, 30, 2), 1, 128, 8, ff=64),
+                               fc.parallel(fc.att(2, 2, 8, 16, 5, 1), 2, 96, 8)], width=64, vocab=67, mult=0.7),
+    "head_200_states_70_200": fc.config([fc.parallel(fc.att(1, 1, 16, 16, 9, 0), 1, 200, 4, ls=0.3, rs=1.0),
+                                         fc.mamba(40, 70, 3, 2), fc.mamba(24, 200, 2, 3, ff=32)], width=32, vocab=53,
+                                        mult=0.8),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(BIG))
+def test_large_heads_and_states(name, dtype):
+    cfg = BIG[name]
+    w = fc.make_weights(cfg, 15, stored(dtype))
+    toks = fc.tokens_for(cfg, 300, 60)
+    ref = {"a": fc.oracle(cfg, w, toks)}
+    eng = fc.build_engine(cfg, w, dtype, max_tokens=320, block_size=16)
+    steps = [([("a", toks[:270], list(range(0, 270, 9)) + [269])], []), ([("a", toks[270:290], list(range(20)))], [])]
+    steps += [([("a", [t], [0])], []) for t in toks[290:]]
+    compare(run(eng, steps), ref, dtype, name)
+
+
 def test_graph_replay_equals_eager_steps():
     """Decode steps replayed from CUDA graphs (padded to four requests and a context bucket, the
     padding rows on the spare state slot) give what the same steps give launched one by one."""
