@@ -208,15 +208,16 @@ def test_window_and_kept_keys_to_the_token(layout, dtype):
     compare(run(eng, steps), {"a": ref}, dtype, "edges, decoded")
 
 
-@pytest.mark.parametrize("dim,window,keep", [(64, 150, 70), (128, 200, 3), (64, 64, 64), (128, 130, 129)])
-def test_tensor_core_attention_with_kept_keys(dim, window, keep):
+@pytest.mark.parametrize("dim,window,keep,heads,kv", [(64, 150, 70, 4, 2), (128, 200, 3, 4, 2), (64, 64, 64, 4, 1),
+                                                      (128, 130, 129, 3, 3), (64, 100, 17, 8, 1)])
+def test_tensor_core_attention_with_kept_keys(dim, window, keep, heads, kv):
     """bfloat16 with head sizes the mma kernels take, windows and kept keys longer than their key
     tiles (64 keys in prompt portions, 16 in decode steps, splits of 128).  Two requests side by
     side, with marked keys as above: `edge` has them window + 5 apart behind the kept keys (the query
     window - 1 behind one sees it, the next does not), `kept` has one at the last kept place.  Whole
     prompts of 300 tokens, portions (more than 8 tokens take the prefill shape, fewer the decode
     shape), then 130 single-token steps for both at once."""
-    cfg = fc.config([fc.parallel(fc.att(4, 2, dim, dim, window, keep, scale=96.0 / dim), 2, 16, 4, ls=1.0, rs=0.2,
+    cfg = fc.config([fc.parallel(fc.att(heads, kv, dim, dim, window, keep, scale=96.0 / dim), 2, 16, 4, ls=1.0, rs=0.2,
                                  ff=48)], width=48, vocab=97, mult=0.9)
     w = fc.marked(cfg, fc.make_weights(cfg, 13, torch.bfloat16), MARK)
     base = [t if t != MARK else MARK + 1 for t in fc.tokens_for(cfg, 430, 7)]
@@ -381,6 +382,13 @@ def test_greedy_generation_through_the_scheduler(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(cfg))
     write_safetensors(tmp_path / "model.safetensors", w)
     prompts = [fc.tokens_for(cfg, n, 40 + i) for i, n in enumerate((37, 3, 21, 50, 9))]
+    # bfloat16: the same path with the storage type a served model has; rounding may pick another token
+    # where two logits are close, so only the shape of the answer is checked
+    llm16 = LLM(str(tmp_path), dtype="bfloat16", ctx=128, block_size=8, prefill_chunk=16, parallel=3)
+    got16 = llm16.generate(prompts, max_tokens=12, temperature=0.7, top_k=20, seed=5)
+    assert all(len(g) == 12 and all(0 <= t < cfg["vocab"] for t in g) for g in got16)
+    assert not llm16.engine.cache.requests
+    del llm16
     llm = LLM(str(tmp_path), dtype="float32", ctx=128, block_size=8, prefill_chunk=16, parallel=3)
     got = llm.generate(prompts, max_tokens=12)
     for p, g in zip(prompts, got):
