@@ -104,18 +104,19 @@ def weight_bytes(model):
 
 
 def falalix_shape(width: int) -> dict:
-    """A Falalix configuration with layer sizes of a real model of that width: the cycle Mamba
-    (no feed-forward), parallel, parallel, Mamba, parallel, parallel, the layers 1..3 run twice."""
+    """A Falalix configuration with layer sizes of a real model of that width: parallel, parallel,
+    Mamba (no feed-forward) run twice as a loop, then the same three layers once more with weights of
+    their own: nine layer runs."""
     mamba = {"type": "mamba1", "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}, "mlp": None}
     heads = max(8, width // 128)
     par = {"type": "parallel",
            "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
-                              "mask": {"size": 1024, "keep_first": 4}, "scale": 128 ** -0.5},
+                              "mask": {"size": 1024, "keep_first": 8}, "scale": 128 ** -0.5},
                      "right": {"heads": width // 64, "dim": 64, "decay_rank": 64},
-                     "left_scale": 0.6, "right_scale": 0.9},
+                     "left_scale": 0.7, "right_scale": 0.8},
            "mlp": {"kind": "dense", "ff": 3 * width}}
-    return {"architecture": "Falalix", "vocab": 32768, "width": width, "layers": [mamba, par, par, mamba, par, par],
-            "loop": {"start": 1, "stop": 4, "times": 2}, "norm": {"eps": 1e-6}, "residual_mult": 0.3}
+    return {"architecture": "Falalix", "vocab": 32768, "width": width, "layers": [par, par, mamba, par, par, mamba],
+            "loop": {"start": 0, "stop": 3, "times": 2}, "norm": {"eps": 1e-6}, "residual_mult": 0.5}
 
 
 def qwen3_shape(width: int, layers: int) -> dict:
