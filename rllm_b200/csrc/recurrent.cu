@@ -409,7 +409,7 @@ RLLM_API int rllm_token_shift(const void* h, int act_dt, const float* mu, const 
 // PASS 0: whole requests.  1: end state from a zero start and the product of the decays, no output.
 // 2: from the carried start state, with output.
 template <typename TA, int DMAX, int PASS>
-__global__ void __launch_bounds__(WKV_PARTS * DMAX / WKV_COLS)
+__global__ void __launch_bounds__(WKV_PARTS * DMAX / WKV_COLS, DMAX <= 64 ? 4 : 1)
 wkv_kernel(const float* rp, const float* kp, const float* vp, const float* wraw, const float* gp, long long ld,
            const float* __restrict__ w0, const float* __restrict__ u, const float* __restrict__ norm_w, float eps,
            float* state, long long slot_stride, long long prev_off, const TA* h, int width,
