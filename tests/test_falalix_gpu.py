@@ -350,6 +350,29 @@ def test_large_heads_and_states(name, dtype):
     compare(run(eng, steps), ref, dtype, name)
 
 
+REAL = fc.config([fc.mamba(2048, 16, 64, 4), fc.parallel(fc.att(8, 2, 128, 128, 96, 4), 16, 64, 64, ls=0.7, rs=0.8, ff=3072),
+                  fc.parallel(fc.att(8, 4, 64, 96, 80, 0), 8, 128, 32, ls=0.9, rs=0.6, ff=2048)],
+                 width=1024, vocab=1531, loop=(0, 2, 2), mult=0.5)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_layer_sizes_of_a_real_model(dtype):
+    """Width 1,024, layers of real sizes (Mamba of 2,048 channels; attention heads of 128 with a window
+    and kept keys beside 16 time-mixing heads of 64; heads of 64 / 96 beside time-mixing heads of 128), the
+    first two layers run twice: the products then take the library, the tcgen05 and the weight-streaming
+    kernels, the attention the mma kernels with kept keys, the recurrences their cut along time.  A
+    prompt of 300 tokens, a portion of 40 beside another request's 20, then single tokens of both."""
+    cfg = REAL
+    w = fc.make_weights(cfg, 16, stored(dtype))
+    toks = {"a": fc.tokens_for(cfg, 352, 70), "b": fc.tokens_for(cfg, 32, 71)}
+    refs = {r: fc.oracle(cfg, w, t) for r, t in toks.items()}
+    eng = fc.build_engine(cfg, w, dtype, max_tokens=512, block_size=32, max_requests=2)
+    steps = [([("a", toks["a"][:300], list(range(0, 300, 23)) + [299])], []),
+             ([("a", toks["a"][300:340], list(range(40))), ("b", toks["b"][:20], [0, 19])], [])]
+    steps += [([("a", [toks["a"][340 + i]], [0]), ("b", [toks["b"][20 + i]], [0])], []) for i in range(12)]
+    compare(run(eng, steps), refs, dtype, "real layer sizes")
+
+
 def test_graph_replay_equals_eager_steps():
     """Decode steps replayed from CUDA graphs (padded to four requests and a context bucket, the
     padding rows on the spare state slot) give what the same steps give launched one by one."""
