@@ -74,6 +74,8 @@ class PagedGroup:
         """(keys, values) of one run entry: [pages, kv_heads, block_size, head size]."""
         if self.pool is not None:
             return self.pool[plane, 0], self.pool[plane, 1]
+        if self.pool_v is None:                        # the values lie in the key rows
+            return self.pool_k[plane], self.pool_k[plane]
         return self.pool_k[plane], self.pool_v[plane]
 
 
@@ -170,7 +172,10 @@ class CacheManager:
     def allocate_device(self, device, dtype) -> None:
         for grp in self.paged:
             n = grp.need
-            if n.value_dim == n.head_dim:
+            if n.values_in_keys:
+                grp.pool_k = torch.zeros((len(grp.entries), grp.n_blocks, n.num_kv_heads, self.block_size,
+                                          n.head_dim), dtype=dtype, device=device)
+            elif n.value_dim == n.head_dim:
                 grp.pool = torch.zeros((len(grp.entries), 2, grp.n_blocks, n.num_kv_heads, self.block_size,
                                         n.head_dim), dtype=dtype, device=device)
             else:
@@ -196,7 +201,8 @@ class CacheManager:
         return total
 
     def bytes_per_token(self, element_size: int) -> int:
-        return sum(len(g.entries) * g.need.num_kv_heads * (g.need.head_dim + g.need.value_dim) * element_size
+        return sum(len(g.entries) * g.need.num_kv_heads
+                   * (g.need.head_dim + (0 if g.need.values_in_keys else g.need.value_dim)) * element_size
                    for g in self.paged)
 
     # ------------------------------------------------------------------ requests

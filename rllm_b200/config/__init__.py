@@ -1,12 +1,14 @@
 from .base import (ConfigError, LayerSpec, ModelConfig, ModelSpec, PartSpec, RunEntry)
 from .falalix import FalalixConfig
+from .govopel import GovopelConfig
 from .qwen3 import Qwen3Config
 from .registry import (config_class, config_from_dict, load_config, register_architecture,
                        supported_architectures)
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config)
 register_architecture("Falalix", FalalixConfig)
+register_architecture("Govopel", GovopelConfig)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config", "FalalixConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "RunEntry", "Qwen3Config", "FalalixConfig", "GovopelConfig",
            "config_class", "config_from_dict", "load_config", "register_architecture",
            "supported_architectures"]

@@ -1,5 +1,5 @@
 // Paged causal attention, plain form: one block per (token, query head), float32
-// arithmetic, any head size that is a multiple of 2 up to 512, any page size, any
+// arithmetic, any head size up to 512 (keys: 2048), any page size, any
 // number of heads and groups, optional sliding window.  It is the float32 path of
 // the engine and the reference the tensor-core kernels are tested against.
 //
@@ -9,7 +9,12 @@
 // without position encoding in the scores sees no difference).  The keys of the step's own
 // tokens are already in the cache.  Key p lives in page block_table[r][p / bs] at
 // offset p % bs; cache layouts [page][kv_head][bs][hd] for keys and [page][kv_head][bs][hdv]
-// for values (the value heads may have another size; the output is [n, H * hdv]).
+// for values (the value heads may have another size; the output is [n, H * hdv]).  Value rows lie
+// v_ld elements apart (hdv when they have a pool of their own; the key rows' length when the values
+// are the leading entries of the key rows themselves, v_cache == k_cache).
+// chunk > 0: positions are cut into runs of `chunk` counted from 0 and a token sees only the keys of
+// its own run (p >= pos - pos % chunk).  softcap > 0: a score s becomes softcap * tanh(s / softcap)
+// before the softmax.
 //
 // Formula: crates/rllm-cpu/src/lib.rs:389-425 of AxiomOperator/rllm; its device
 // counterpart is paged_attention (crates/rllm-cuda/kernels/kernels.cu:1634-1690).
@@ -19,7 +24,7 @@
 #include <math.h>
 
 #define ATT_THREADS 128
-#define ATT_MAX_ACC 4   // hd <= ATT_THREADS * ATT_MAX_ACC
+#define ATT_MAX_ACC 4   // value heads: hdv <= ATT_THREADS * ATT_MAX_ACC (key heads up to 2048)
 
 template <typename TQ, typename TC, typename TO>
 __global__ void __launch_bounds__(ATT_THREADS)
@@ -28,7 +33,7 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
                                const int* __restrict__ positions, const int* __restrict__ seq_ids,
                                const int* __restrict__ block_table, int table_stride, int H, int K,
                                int hd, int hdv, int bs, float scale, int window, int keep_first, int n_pages,
-                               int* err) {
+                               int* err, int chunk, float softcap, int v_ld) {
     extern __shared__ float smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -41,7 +46,8 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
     const int kvh = h / (H / K);
     const int pos = positions[t];
     const int* table = block_table + (size_t)seq_ids[t] * table_stride;
-    const int first = (window > 0 && pos + 1 - window > 0) ? pos + 1 - window : 0;
+    int first = (window > 0 && pos + 1 - window > 0) ? pos + 1 - window : 0;
+    if (chunk > 0) first = max(first, pos - pos % chunk);
     const int tid = threadIdx.x;
 
     const TQ* qrow = q + ((size_t)t * H + h) * hd;
@@ -72,6 +78,7 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
             float dot = 0.f;
             for (int i = 0; i < hd; ++i) dot += qs[i] * to_f<TC>(kr[i]);
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         const float cmax = block_max(s, red);
         const float m_new = fmaxf(m_run, cmax);
@@ -87,7 +94,7 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
             const int d = tid + a * ATT_THREADS;
             if (d < hdv) {
                 float v = acc[a] * alpha;
-                for (int j = 0; j < cn; ++j) v += pr[j] * to_f<TC>(v_cache[(size_t)rowoff[j] * hdv + d]);
+                for (int j = 0; j < cn; ++j) v += pr[j] * to_f<TC>(v_cache[(size_t)rowoff[j] * v_ld + d]);
                 acc[a] = v;
             }
         }
@@ -108,9 +115,12 @@ RLLM_API int rllm_paged_attention_generic(const void* q, int q_dtype, const void
                                           int out_dtype, const int* positions, const int* seq_ids,
                                           const int* block_table, int table_stride, int n, int H,
                                           int K, int hd, int hdv, int bs, float scale, int window, int keep_first,
-                                          int n_pages, int* err, cudaStream_t stream) {
+                                          int n_pages, int* err, int chunk, float softcap, int v_ld,
+                                          cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (hd > ATT_THREADS * ATT_MAX_ACC || hdv > ATT_THREADS * ATT_MAX_ACC || hdv <= 0 || K <= 0 || H % K != 0 ||
+    if (v_ld <= 0) v_ld = hdv;
+    if (chunk < 0 || v_ld < hdv) return (int)cudaErrorInvalidValue;
+    if (hd > 2048 || hdv > ATT_THREADS * ATT_MAX_ACC || hdv <= 0 || K <= 0 || H % K != 0 ||
         bs <= 0 || keep_first < 0)
         return (int)cudaErrorInvalidValue;
     if (q_dtype != cache_dtype || q_dtype != out_dtype) return (int)cudaErrorInvalidValue;
@@ -120,10 +130,11 @@ RLLM_API int rllm_paged_attention_generic(const void* q, int q_dtype, const void
         return rllm_launch(paged_attention_generic_kernel<float, float, float>, grid, dim3(ATT_THREADS), smem,
                            stream, (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out,
                            positions, seq_ids, block_table, table_stride, H, K, hd, hdv, bs, scale, window, keep_first, n_pages,
-                           err);
+                           err, chunk, softcap, v_ld);
     return rllm_launch(paged_attention_generic_kernel<bf16, bf16, bf16>, grid, dim3(ATT_THREADS), smem, stream,
                        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions,
-                       seq_ids, block_table, table_stride, H, K, hd, hdv, bs, scale, window, keep_first, n_pages, err);
+                       seq_ids, block_table, table_stride, H, K, hd, hdv, bs, scale, window, keep_first, n_pages, err,
+                       chunk, softcap, v_ld);
 }
 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches

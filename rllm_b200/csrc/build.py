@@ -31,7 +31,7 @@ NVCC_FLAGS = [
 
 # library name -> (sources, extra link flags)
 LIBRARIES = {
-    "core": (["elementwise.cu", "rowwise.cu", "attention_generic.cu", "gemm_plain.cu", "sampling.cu"], []),
+    "core": (["elementwise.cu", "rowwise.cu", "headwise.cu", "attention_generic.cu", "gemm_plain.cu", "sampling.cu"], []),
     "recur": (["recurrent.cu"], []),
     "blas": (["gemm_lib.cu"], ["-lcublas"]),
     "fast": (["skinny_gemm.cu"], []),

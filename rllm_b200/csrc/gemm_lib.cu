@@ -49,5 +49,25 @@ RLLM_API int rllm_gemm_lib(const void* A, const void* W, void* C, int c_dtype, i
     return s == CUBLAS_STATUS_SUCCESS ? 0 : 10000 + (int)s;
 }
 
+// A batch of independent products (operand b at A + b * sa, W + b * sw, C + b * sc, in elements)
+// through cublasGemmStridedBatchedEx: the per-head products of attention through latents.
+RLLM_API int rllm_gemm_lib_batched(const void* A, const void* W, void* C, int c_dtype, int m, int n, int k,
+                                   int lda, int ldw, int ldc, int batch, long long sa, long long sw, long long sc,
+                                   cudaStream_t stream) {
+    if (m <= 0 || n <= 0 || batch <= 0) return 0;
+    if (k <= 0) return (int)cudaErrorInvalidValue;
+    cublasHandle_t h;
+    int st = get_handle(&h);
+    if (st) return st;
+    if (cublasSetStream(h, stream) != CUBLAS_STATUS_SUCCESS) return 10003;
+    const float alpha = 1.f, beta = 0.f;
+    cublasStatus_t s = cublasGemmStridedBatchedEx(h, CUBLAS_OP_T, CUBLAS_OP_N, n, m, k, &alpha, W, CUDA_R_16BF, ldw, sw,
+                                                  A, CUDA_R_16BF, lda, sa, &beta, C,
+                                                  c_dtype == RLLM_F32 ? CUDA_R_32F : CUDA_R_16BF, ldc, sc, batch,
+                                                  CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+    return s == CUBLAS_STATUS_SUCCESS ? 0 : 10000 + (int)s;
+}
+
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_gemm_lib)
+RLLM_PACKED(rllm_gemm_lib_batched)

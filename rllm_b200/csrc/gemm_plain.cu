@@ -20,11 +20,14 @@
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(const TA* A, const TW* __restrict__ W, TC* C, int m,
-                  int n, int k, int lda, int ldw, int ldc, int accumulate) {
+                  int n, int k, int lda, int ldw, int ldc, int accumulate, long long sa, long long sw, long long sc) {
     __shared__ float As[TK][TM + 1];
     __shared__ float Ws[TK][TN + 1];
     pdl_wait();
     pdl_launch_dependents();
+    A += (size_t)blockIdx.z * sa;                 // a batch of products: one per z, operands sa / sw / sc apart
+    W += (size_t)blockIdx.z * sw;
+    C += (size_t)blockIdx.z * sc;
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;        // 16 x 16 threads, 4 x 4 outputs each
     const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
@@ -75,16 +78,20 @@ gemm_plain_kernel(const TA* A, const TW* __restrict__ W, TC* C, int m,
     }
 }
 
-RLLM_API int rllm_gemm_plain(const void* A, int a_dtype, const void* W, int w_dtype, void* C,
-                             int c_dtype, int m, int n, int k, int lda, int ldw, int ldc,
-                             int accumulate, cudaStream_t stream) {
-    if (m <= 0 || n <= 0) return 0;
-    if (k <= 0) return (int)cudaErrorInvalidValue;
+// A batch of `batch` independent products, operand b at A + b * sa, W + b * sw, C + b * sc (elements):
+// the per-head products of attention through latents (heads as the batch, rows strided by the
+// token's whole row).
+RLLM_API int rllm_gemm_plain_batched(const void* A, int a_dtype, const void* W, int w_dtype, void* C,
+                                     int c_dtype, int m, int n, int k, int lda, int ldw, int ldc,
+                                     int accumulate, int batch, long long sa, long long sw, long long sc,
+                                     cudaStream_t stream) {
+    if (m <= 0 || n <= 0 || batch <= 0) return 0;
+    if (k <= 0 || batch > 65535) return (int)cudaErrorInvalidValue;
     if (accumulate && c_dtype != RLLM_F32) return (int)cudaErrorInvalidValue;
-    dim3 grid((n + TN - 1) / TN, (m + TM - 1) / TM);
+    dim3 grid((n + TN - 1) / TN, (m + TM - 1) / TM, batch);
 #define LAUNCH(TA, TW, TC)                                                                        \
     return rllm_launch(gemm_plain_kernel<TA, TW, TC>, grid, dim3(256), 0, stream, (const TA*)A,    \
-                       (const TW*)W, (TC*)C, m, n, k, lda, ldw, ldc, accumulate)
+                       (const TW*)W, (TC*)C, m, n, k, lda, ldw, ldc, accumulate, sa, sw, sc)
     const int key = a_dtype * 4 + w_dtype * 2 + c_dtype;
     switch (key) {
         case 0: LAUNCH(float, float, float); break;
@@ -101,5 +108,13 @@ RLLM_API int rllm_gemm_plain(const void* A, int a_dtype, const void* W, int w_dt
     return 0;
 }
 
+RLLM_API int rllm_gemm_plain(const void* A, int a_dtype, const void* W, int w_dtype, void* C,
+                             int c_dtype, int m, int n, int k, int lda, int ldw, int ldc,
+                             int accumulate, cudaStream_t stream) {
+    return rllm_gemm_plain_batched(A, a_dtype, W, w_dtype, C, c_dtype, m, n, k, lda, ldw, ldc, accumulate, 1, 0, 0, 0,
+                                   stream);
+}
+
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_gemm_plain)
+RLLM_PACKED(rllm_gemm_plain_batched)

@@ -1,0 +1,263 @@
+// Kernels of layers that norm a sublayer's OUTPUT, of attention whose queries and keys are rotated
+// first and normed afterwards, and of attention through low-rank latents.  float32 arithmetic
+// whatever the storage type; accurate expf / tanhf / sqrtf (no fast-math).
+//
+//   norm_rows          v = in[t] / rms(in[t]) * w  (+ x[t]);  x[t] = v (float32, optional);
+//                      low[t] = v in the activation type (optional).  The embedding's norm, the norm
+//                      of a sublayer's output joining the stream, the norm of a latent.
+//   rope_unitnorm_store  per head of a [q | k] projection row: rotate the first `rot` entries by the
+//                      step's angles (pairs (i, i + rot/2)), then divide the head by its root mean
+//                      square; queries out, keys into the paged cache; the values written beside them
+//                      are the key heads as projected (before rotation and norm), or the columns that
+//                      follow the keys when the row has them.
+//   latent_rope_store  one cache row per token [normed latent (rank) | rotated shared key part (r)],
+//                      and the rotated part of every query head copied behind that head's latent-space
+//                      query.
+//   glu_clamped        out = g * sigmoid(alpha * g) * (u + shift), g = min(gate, limit),
+//                      u = clamp(up, -limit, limit).
+//   softcap_rows       x = cap * tanh(x / cap) in place.
+//
+// Angles come from a table of (cos, sin) per token and pair (rope_table: once per pass).  A slot < 0
+// writes nothing to the cache; a slot beyond the pool sets the error word.
+#include "common.cuh"
+#include <math.h>
+
+__device__ __forceinline__ float ld_dt(const void* p, int dt, size_t i) {
+    return dt == RLLM_F32 ? ((const float*)p)[i] : __bfloat162float(((const bf16*)p)[i]);
+}
+__device__ __forceinline__ void st_dt(void* p, int dt, size_t i, float v) {
+    if (dt == RLLM_F32) ((float*)p)[i] = v;
+    else ((bf16*)p)[i] = __float2bfloat16_rn(v);
+}
+
+// ------------------------------------------------------------------ norm of rows, joined to the stream
+// One block per row.  `in` may be x itself (add == 0: x is normed in place).
+__global__ void __launch_bounds__(256)
+norm_rows_kernel(const void* in, int in_dt, long long ld_in, const float* __restrict__ w, float* x, int add,
+                 void* low, int low_dt, long long ld_low, int d, float eps) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = ld_dt(in, in_dt, t * ld_in + i);
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = ld_dt(in, in_dt, t * ld_in + i) * rs * (w ? w[i] : 1.f);
+        if (x) {
+            if (add) v += x[t * d + i];
+            x[t * d + i] = v;
+        }
+        if (low) st_dt(low, low_dt, t * ld_low + i, v);
+    }
+}
+
+RLLM_API int rllm_norm_rows(const void* in, int in_dt, long long ld_in, const float* w, float* x, int add, void* low,
+                            int low_dt, long long ld_low, int n, int d, float eps, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || ld_in < d || (low && ld_low < d)) return (int)cudaErrorInvalidValue;
+    return rllm_launch(norm_rows_kernel, dim3(n), dim3(d >= 1024 ? 256 : 128), 0, stream, in, in_dt, ld_in, w, x, add,
+                       low, low_dt, ld_low, d, eps);
+}
+
+// ------------------------------------------------------------------ rotate, then unit norm, then store
+// Grid (token, group of 4 heads), one warp per head; heads 0..H-1 are queries, H..H+G-1 keys.
+// row = [q (H*hd) | k (G*hd) | v (G*hd, only when v_tied == 0)], rows ld apart.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128)
+rope_unitnorm_store_kernel(const TI* row_base, long long ld, const float2* cs_table, int rot, float cs_mult,
+                           const int* __restrict__ slots, TO* q_out, TO* k_cache, TO* v_cache, int H, int G, int hd,
+                           int bs, float eps, int unit_norm, int v_tied, int write_kv, int n_slots, int* err) {
+    extern __shared__ float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * 4 + warp;
+    if (head >= H + G) return;
+    float* v = sm + (size_t)warp * hd;
+    const TI* src = row_base + (size_t)t * ld + (size_t)head * hd;
+    for (int i = lane; i < hd; i += 32) v[i] = to_f<TI>(src[i]);
+    __syncwarp();
+    const bool is_key = head >= H;
+    int slot = -1;
+    if (is_key && write_kv) {
+        slot = slots[t];
+        if (slot >= n_slots) {
+            if (lane == 0 && err) atomicExch(err, RLLM_ERR_SLOT);
+            slot = -1;
+        }
+    }
+    const size_t cache_row = slot < 0 ? 0 : (((size_t)(slot / bs) * G + (head - H)) * bs + slot % bs) * hd;
+    if (is_key && slot >= 0) {
+        // the values: the key head as projected, or the row's own value columns
+        const TI* vs = v_tied ? src : src + (size_t)G * hd;
+        for (int i = lane; i < hd; i += 32) v_cache[cache_row + i] = from_f<TO>(to_f<TI>(vs[i]));
+    }
+    const int half = rot >> 1;
+    const float2* cs = cs_table + (size_t)t * half;
+    for (int i = lane; i < half; i += 32) {
+        const float2 a = cs[i];
+        const float c = a.x * cs_mult, s = a.y * cs_mult;
+        const float u = v[i], w = v[i + half];
+        v[i] = u * c - w * s;
+        v[i + half] = w * c + u * s;
+    }
+    __syncwarp();
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) ss += v[i] * v[i];
+    ss = warp_sum(ss);
+    const float rs = unit_norm ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.f;
+    if (!is_key) {
+        TO* dst = q_out + ((size_t)t * H + head) * hd;
+        for (int i = lane; i < hd; i += 32) dst[i] = from_f<TO>(v[i] * rs);
+    } else if (slot >= 0) {
+        for (int i = lane; i < hd; i += 32) k_cache[cache_row + i] = from_f<TO>(v[i] * rs);
+    }
+}
+
+RLLM_API int rllm_rope_unitnorm_store(const void* rows, int in_dt, long long ld, const void* cs_table, int rot,
+                                      float cs_mult, const int* slots, void* q_out, void* k_cache, void* v_cache,
+                                      int out_dt, int n, int H, int G, int hd, int bs, float eps, int unit_norm,
+                                      int v_tied, int write_kv, long long n_slots, int* err, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (H <= 0 || G <= 0 || hd <= 0 || rot < 0 || rot > hd || (rot & 1) || bs <= 0 || (rot && !cs_table) ||
+        ld < (long long)(H + G * (v_tied ? 1 : 2)) * hd)
+        return (int)cudaErrorInvalidValue;
+    const int ns = (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots);
+    const dim3 grid(n, (H + G + 3) / 4);
+    const size_t smem = (size_t)4 * hd * sizeof(float);
+#define LAUNCH(TI, TO)                                                                                          \
+    return rllm_launch(rope_unitnorm_store_kernel<TI, TO>, grid, dim3(128), smem, stream, (const TI*)rows, ld,   \
+                       (const float2*)cs_table, rot, cs_mult, slots, (TO*)q_out, (TO*)k_cache, (TO*)v_cache, H, G, \
+                       hd, bs, eps, unit_norm, v_tied, write_kv, ns, err)
+    if (in_dt == RLLM_F32 && out_dt == RLLM_F32) { LAUNCH(float, float); }
+    if (in_dt == RLLM_F32 && out_dt == RLLM_BF16) { LAUNCH(float, bf16); }
+    if (in_dt == RLLM_BF16 && out_dt == RLLM_BF16) { LAUNCH(bf16, bf16); }
+    return (int)cudaErrorInvalidValue;
+#undef LAUNCH
+}
+
+// ------------------------------------------------------------------ latent attention: cache row and query parts
+// One block per token.  kv[t] = [latent (rank) | shared key part (r)] with rows ld_kv apart (float32);
+// the latent is RMS-normed with a weight, the key part rotated (pairs (i, i + r/2)); both go to the
+// token's cache row [rank + r] (one key/value head).  q[t] = H heads of [plain (dq) | rotated (r)]
+// with rows ld_q apart; the rotated part of head h goes to q_att[t, h, rank : rank + r] (the first
+// rank entries of each head are written by the product that takes the plain part into latent space).
+template <typename TQ, typename TO>
+__global__ void __launch_bounds__(256)
+latent_rope_store_kernel(const TQ* q, long long ld_q, const float* kv, long long ld_kv,
+                         const float* __restrict__ kv_norm_w, const float2* cs_table, float cs_mult,
+                         const int* __restrict__ slots, TO* q_att, TO* cache, int H, int dq, int r, int rank, int bs,
+                         float eps, int write_kv, int n_slots, int* err) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const int half = r >> 1, W = rank + r;
+    const float2* cs = cs_table + (size_t)t * half;
+    // queries: every (head, pair)
+    for (int i = tid; i < H * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        const TQ* src = q + (size_t)t * ld_q + (size_t)h * (dq + r) + dq;
+        const float2 a = cs[j];
+        const float c = a.x * cs_mult, s = a.y * cs_mult;
+        const float u = to_f<TQ>(src[j]), w = to_f<TQ>(src[j + half]);
+        TO* dst = q_att + ((size_t)t * H + h) * W + rank;
+        dst[j] = from_f<TO>(u * c - w * s);
+        dst[j + half] = from_f<TO>(w * c + u * s);
+    }
+    const float* row = kv + (size_t)t * ld_kv;
+    float ss = 0.f;
+    for (int i = tid; i < rank; i += blockDim.x) ss += row[i] * row[i];
+    ss = block_sum(ss, red);
+    if (!write_kv) return;
+    int slot = slots[t];
+    if (slot >= n_slots) {
+        if (tid == 0 && err) atomicExch(err, RLLM_ERR_SLOT);
+        slot = -1;
+    }
+    if (slot < 0) return;
+    const float rs = 1.0f / sqrtf(ss / (float)rank + eps);
+    TO* dst = cache + (size_t)slot * W;                 // one head: page * bs + offset is the row
+    for (int i = tid; i < rank; i += blockDim.x) dst[i] = from_f<TO>(row[i] * rs * kv_norm_w[i]);
+    for (int j = tid; j < half; j += blockDim.x) {
+        const float2 a = cs[j];
+        const float c = a.x * cs_mult, s = a.y * cs_mult;
+        const float u = row[rank + j], w = row[rank + j + half];
+        dst[rank + j] = from_f<TO>(u * c - w * s);
+        dst[rank + j + half] = from_f<TO>(w * c + u * s);
+    }
+}
+
+RLLM_API int rllm_latent_rope_store(const void* q, int q_dt, long long ld_q, const float* kv, long long ld_kv,
+                                    const float* kv_norm_w, const void* cs_table, float cs_mult, const int* slots,
+                                    void* q_att, void* cache, int out_dt, int n, int H, int dq, int r, int rank,
+                                    int bs, float eps, int write_kv, long long n_slots, int* err,
+                                    cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (H <= 0 || dq <= 0 || r <= 0 || (r & 1) || rank <= 0 || bs <= 0 || !cs_table || !kv_norm_w ||
+        ld_q < (long long)H * (dq + r) || ld_kv < rank + r)
+        return (int)cudaErrorInvalidValue;
+    const int ns = (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots);
+#define LAUNCH(TQ, TO)                                                                                           \
+    return rllm_launch(latent_rope_store_kernel<TQ, TO>, dim3(n), dim3(256), 0, stream, (const TQ*)q, ld_q, kv,   \
+                       ld_kv, kv_norm_w, (const float2*)cs_table, cs_mult, slots, (TO*)q_att, (TO*)cache, H, dq, r, \
+                       rank, bs, eps, write_kv, ns, err)
+    if (q_dt == RLLM_F32 && out_dt == RLLM_F32) { LAUNCH(float, float); }
+    if (q_dt == RLLM_F32 && out_dt == RLLM_BF16) { LAUNCH(float, bf16); }
+    if (q_dt == RLLM_BF16 && out_dt == RLLM_BF16) { LAUNCH(bf16, bf16); }
+    return (int)cudaErrorInvalidValue;
+#undef LAUNCH
+}
+
+// ------------------------------------------------------------------ clamped gated activation
+// gate_up[t] = [gate (F) | up (F)] with rows ld apart.
+__global__ void glu_clamped_kernel(const void* gate_up, int in_dt, long long ld, void* out, int out_dt, int F,
+                                   float limit, float alpha, float shift, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / F;
+    const int c = (int)(i - t * F);
+    float g = ld_dt(gate_up, in_dt, t * ld + c), u = ld_dt(gate_up, in_dt, t * ld + F + c);
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    st_dt(out, out_dt, i, g / (1.0f + expf(-alpha * g)) * (u + shift));
+}
+
+RLLM_API int rllm_glu_clamped(const void* gate_up, int in_dt, long long ld, void* out, int out_dt, int n, int F,
+                              float limit, float alpha, float shift, cudaStream_t stream) {
+    const size_t total = (size_t)n * F;
+    if (total == 0) return 0;
+    if (ld < 2LL * F) return (int)cudaErrorInvalidValue;
+    return rllm_launch(glu_clamped_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, gate_up,
+                       in_dt, ld, out, out_dt, F, limit, alpha, shift, total);
+}
+
+// ------------------------------------------------------------------ soft cap
+__global__ void softcap_rows_kernel(float* x, float cap, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = cap * tanhf(x[i] / cap);
+}
+
+RLLM_API int rllm_softcap_rows(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+    return rllm_launch(softcap_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, cap,
+                       (size_t)total);
+}
+
+RLLM_PACKED(rllm_norm_rows)
+RLLM_PACKED(rllm_rope_unitnorm_store)
+RLLM_PACKED(rllm_latent_rope_store)
+RLLM_PACKED(rllm_glu_clamped)
+RLLM_PACKED(rllm_softcap_rows)

@@ -344,29 +344,124 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, q_ou
 # ------------------------------------------------------------------ attention
 
 def paged_attention_generic(q, k_cache, v_cache, out, positions, seq_ids, block_table, H, K, hd,
-                            block_size, scale, window=0, keep_first=0, v_head_dim=None):
+                            block_size, scale, window=0, keep_first=0, v_head_dim=None, chunk=0, softcap=0.0):
     """Plain paged causal attention; q [n, H*hd], out [n, H*hdv], caches [pages, K, block_size, hd] and
     [pages, K, block_size, hdv] (hdv = v_head_dim, hd by default).  keep_first: the first keys of a
-    request stay visible when the window has passed them."""
+    request stay visible when the window has passed them.  chunk: a token sees only the keys of its
+    own run of that many positions (counted from 0).  softcap: scores go through cap * tanh(s / cap).
+    `v_cache is k_cache` with hdv < hd: the values are the first hdv entries of the key rows."""
     _need_cuda(q, k_cache, v_cache, out, positions, seq_ids, block_table)
     _need_contig(q=q, k_cache=k_cache, v_cache=v_cache, out=out, positions=positions, seq_ids=seq_ids)
     n = q.shape[0]
     hdv = hd if not v_head_dim else int(v_head_dim)
     assert q.shape == (n, H * hd) and out.shape == (n, H * hdv)
-    assert k_cache.shape[-1] == hd and v_cache.shape[-1] == hdv
+    v_ld = hd if (v_cache.data_ptr() == k_cache.data_ptr() and hdv < hd) else hdv
+    assert k_cache.shape[-1] == hd and v_cache.shape[-1] == v_ld >= hdv
     assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.stride(1) == 1
     assert positions.dtype == torch.int32 and seq_ids.dtype == torch.int32
-    if hd > 512 or hdv > 512:
-        raise KernelError(f"head size {max(hd, hdv)} exceeds the attention kernel's limit of 512")
+    if hd > 2048 or hdv > 512:
+        raise KernelError(f"head sizes {hd} (keys) and {hdv} (values) exceed the attention kernel's limits of 2048 and 512")
     if H % K:
         raise KernelError(f"{H} query heads are not a multiple of {K} key/value heads")
     _check(core().rllm_paged_attention_generic(
         _ptr(q), c_int(_code(q)), _ptr(k_cache), _ptr(v_cache), c_int(_code(k_cache)), _ptr(out),
         c_int(_code(out)), _ptr(positions), _ptr(seq_ids), _ptr(block_table), c_int(block_table.stride(0)),
         c_int(n), c_int(H), c_int(K), c_int(hd), c_int(hdv), c_int(block_size), c_float(scale), c_int(window),
-        c_int(keep_first), c_int(min(k_cache.shape[0], 0x7fffffff)), _ptr(error_word(q.device)), _stream()),
+        c_int(keep_first), c_int(min(k_cache.shape[0], 0x7fffffff)), _ptr(error_word(q.device)), c_int(chunk),
+        c_float(softcap), c_int(v_ld), _stream()),
         "paged_attention_generic")
     return out
+
+
+# ------------------------------------------------------------------ output norms, rotate-then-norm heads, latents (headwise.cu)
+
+def norm_rows(rows, weight, eps, x=None, add=False, low=None):
+    """v = rows / rms(rows) * weight (weight None: 1) (+ x when `add`); x (float32 [n, d], optional)
+    takes v; `low` (optional, any row stride) takes v in its own type.  `rows` may be x itself, or
+    columns of a wider matrix."""
+    _need_cuda(rows, weight, x, low)
+    _rows2d(rows, "rows")
+    n, d = rows.shape
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == d and weight.is_contiguous())
+    assert x is None or (x.dtype == torch.float32 and x.shape == (n, d) and x.is_contiguous())
+    assert low is None or _rows2d(low, "low").shape == (n, d)
+    if x is None and low is None:
+        raise KernelError("norm_rows: nowhere to write")
+    _check(core().rllm_norm_rows(_ptr(rows), c_int(_code(rows)), c_longlong(rows.stride(0)), _ptr(weight), _ptr(x),
+                                 c_int(1 if add else 0), _ptr(low), c_int(_code(low) if low is not None else F32),
+                                 c_longlong(low.stride(0) if low is not None else 0), c_int(n), c_int(d), c_float(eps),
+                                 _stream()), "norm_rows")
+    return low if low is not None else x
+
+
+def rope_unitnorm_store(rows, cs_table, rot, cs_mult, slots, q_out, k_cache, v_cache, H, G, hd, block_size, eps,
+                        unit_norm=True, v_tied=True, write_kv=True):
+    """rows [n, (H + G) * hd (+ G * hd values)] -> per head: the first `rot` entries rotated by the
+    angles of cs_table [n, rot/2, 2] (cos and sin times cs_mult), then the head divided by its root mean
+    square (unit_norm); queries to q_out, keys to the paged cache; the values stored are the key heads
+    as projected (v_tied) or the row's value columns.  See headwise.cu."""
+    _need_cuda(rows, cs_table, slots, q_out, k_cache, v_cache)
+    _need_contig(q_out=q_out, k_cache=k_cache, v_cache=v_cache, slots=slots)
+    _rows2d(rows, "rows")
+    n = rows.shape[0]
+    assert rows.shape[1] == (H + G * (1 if v_tied else 2)) * hd and q_out.shape == (n, H * hd)
+    assert slots.dtype == torch.int32 and slots.numel() == n
+    assert k_cache.shape[1:] == (G, block_size, hd) and v_cache.shape[1:] == (G, block_size, hd)
+    assert k_cache.dtype == v_cache.dtype == q_out.dtype
+    assert rot == 0 or (cs_table.dtype == torch.float32 and cs_table.shape == (n, rot // 2, 2) and cs_table.is_contiguous())
+    _check(core().rllm_rope_unitnorm_store(
+        _ptr(rows), c_int(_code(rows)), c_longlong(rows.stride(0)), _ptr(cs_table), c_int(rot), c_float(cs_mult),
+        _ptr(slots), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), c_int(_code(q_out)), c_int(n), c_int(H), c_int(G),
+        c_int(hd), c_int(block_size), c_float(eps), c_int(1 if unit_norm else 0), c_int(1 if v_tied else 0),
+        c_int(1 if write_kv else 0), c_longlong(k_cache.shape[0] * block_size), _ptr(error_word(rows.device)),
+        _stream()), "rope_unitnorm_store")
+    return q_out
+
+
+def latent_rope_store(q, kv, kv_norm_w, cs_table, cs_mult, slots, q_att, cache, H, dq, r, rank, block_size, eps,
+                      write_kv=True):
+    """Attention through latents, the step between the projections and the attention kernel: kv
+    [n, rank + r] (float32, any row stride) -> cache row [normed latent | rotated shared key part];
+    q [n, H * (dq + r)] -> the rotated part of every head into q_att[:, h, rank:rank + r].  See headwise.cu."""
+    _need_cuda(q, kv, kv_norm_w, cs_table, slots, q_att, cache)
+    _need_contig(q_att=q_att, cache=cache, slots=slots)
+    _rows2d(q, "q"), _rows2d(kv, "kv")
+    n = q.shape[0]
+    assert q.shape[1] == H * (dq + r) and kv.shape == (n, rank + r) and kv.dtype == torch.float32
+    assert q_att.shape == (n, H * (rank + r)) and cache.shape[1:] == (1, block_size, rank + r)
+    assert cache.dtype == q_att.dtype and slots.dtype == torch.int32 and slots.numel() == n
+    assert kv_norm_w.dtype == torch.float32 and kv_norm_w.numel() == rank and kv_norm_w.is_contiguous()
+    assert cs_table.dtype == torch.float32 and cs_table.shape == (n, r // 2, 2) and cs_table.is_contiguous()
+    _check(core().rllm_latent_rope_store(
+        _ptr(q), c_int(_code(q)), c_longlong(q.stride(0)), _ptr(kv), c_longlong(kv.stride(0)), _ptr(kv_norm_w),
+        _ptr(cs_table), c_float(cs_mult), _ptr(slots), _ptr(q_att), _ptr(cache), c_int(_code(q_att)), c_int(n),
+        c_int(H), c_int(dq), c_int(r), c_int(rank), c_int(block_size), c_float(eps), c_int(1 if write_kv else 0),
+        c_longlong(cache.shape[0] * block_size), _ptr(error_word(q.device)), _stream()), "latent_rope_store")
+    return q_att
+
+
+def glu_clamped(gate_up, out, limit, alpha=1.0, shift=0.0):
+    """gate_up [n, 2F] (gate columns, then up columns; float32 or bfloat16) -> out [n, F] =
+    g * sigmoid(alpha * g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit)
+    (limit 0: no clamp)."""
+    _need_cuda(gate_up, out)
+    _need_contig(out=out)
+    _rows2d(gate_up, "gate_up")
+    n, F = out.shape
+    assert gate_up.shape == (n, 2 * F)
+    _check(core().rllm_glu_clamped(_ptr(gate_up), c_int(_code(gate_up)), c_longlong(gate_up.stride(0)), _ptr(out),
+                                   c_int(_code(out)), c_int(n), c_int(F), c_float(limit), c_float(alpha),
+                                   c_float(shift), _stream()), "glu_clamped")
+    return out
+
+
+def softcap_rows(x, cap):
+    """x = cap * tanh(x / cap) in place (float32)."""
+    _need_cuda(x)
+    _need_contig(x=x)
+    assert x.dtype == torch.float32
+    _check(core().rllm_softcap_rows(_ptr(x), c_longlong(x.numel()), c_float(cap), _stream()), "softcap_rows")
+    return x
 
 
 # ------------------------------------------------------------------ row-wise helpers (rowwise.cu)
@@ -619,6 +714,39 @@ def gemm_plain(a, w, out, accumulate=False):
                                   c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
                                   c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if accumulate else 0),
                                   _stream()), "gemm_plain")
+    return out
+
+
+def head_linear(a, w, out):
+    """One product per head: out[t, h, :] = w[h] . a[t, h, :] for a [n, H, k], w [H, m, k], out [n, H, m].
+    `a` and `out` may be views into wider rows (a head's columns inside a token's row); their last
+    axis is contiguous.  float32 operands take the plain product, bfloat16 the library's strided batch
+    (float32 accumulation in both)."""
+    _need_cuda(a, w, out)
+    n, H, k = a.shape
+    m = w.shape[1]
+    assert w.shape == (H, m, k) and w.is_contiguous() and out.shape == (n, H, m)
+    assert a.stride(2) == 1 and out.stride(2) == 1
+    if n == 0:
+        return out
+    lib_ok = (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 and a.stride(0) % 8 == 0
+              and a.stride(1) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+              and out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 and out.stride(1) % 8 == 0)
+    if lib_ok:
+        st = _lib("blas").rllm_gemm_lib_batched(
+            _ptr(a), _ptr(w), _ptr(out), c_int(_code(out)), c_int(n), c_int(m), c_int(k), c_int(a.stride(0)), c_int(k),
+            c_int(out.stride(0)), c_int(H), c_longlong(a.stride(1)), c_longlong(m * k), c_longlong(out.stride(1)),
+            _stream())
+        if st >= 10000:
+            raise KernelError(f"head_linear: cuBLAS status {st - 10000} for {H} products of m={n} n={m} k={k}")
+        _check(st, "gemm_lib_batched", own=False)
+        return out
+    if a.dtype != w.dtype:
+        raise KernelError(f"head_linear: activation {a.dtype} and weight {w.dtype} differ")
+    _check(core().rllm_gemm_plain_batched(
+        _ptr(a), c_int(_code(a)), _ptr(w), c_int(_code(w)), _ptr(out), c_int(_code(out)), c_int(n), c_int(m), c_int(k),
+        c_int(a.stride(0)), c_int(k), c_int(out.stride(0)), c_int(0), c_int(H), c_longlong(a.stride(1)),
+        c_longlong(m * k), c_longlong(out.stride(1)), _stream()), "gemm_plain_batched")
     return out
 
 
@@ -1291,16 +1419,16 @@ def attention_tc(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_re
 
 
 def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_size, scale, window=0,
-                    keep_first=0, v_head_dim=None):
+                    keep_first=0, v_head_dim=None, chunk=0, softcap=0.0):
     """Attention of the step's tokens over the paged cache; chooses the kernel by element type,
     head size and the shape of the step (`ctx`: the step's StepContext).  float32, head sizes
     other than 64 and 128 and value heads of another size than the key heads take the plain kernel;
     windows that keep the first keys take the mma.sync kernels, not the tcgen05 one."""
     hdv = hd if not v_head_dim else int(v_head_dim)
     keep_first = keep_first if window else 0
-    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd:
+    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd or chunk or softcap:
         return paged_attention_generic(q, k_cache, v_cache, out, ctx.positions, ctx.seq_ids, block_table,
-                                       H, K, hd, block_size, scale, window, keep_first, hdv)
+                                       H, K, hd, block_size, scale, window, keep_first, hdv, chunk, softcap)
     key = (H // K, window)
     plan = ctx.plans.get(key)
     if plan is None:

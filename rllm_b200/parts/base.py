@@ -65,12 +65,15 @@ class PagedKVNeed:
     """Keys and values in pages.  `window` > 0: only the last `window` keys are ever read, so
     pages that the window has passed can be given back; with `keep_first` > 0 the first that many
     keys of a request stay readable all the same, and their pages are kept.  `v_head_dim`: size of
-    a value head where it differs from a key head (0: the same)."""
+    a value head where it differs from a key head (0: the same).  `values_in_keys` > 0: the values
+    are the first that many entries of the key rows themselves (attention through a latent that
+    serves as key and value); there is no pool of values then, and a view's `v` is its `k`."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     keep_first: int = 0
     v_head_dim: int = 0
+    values_in_keys: int = 0
 
     @property
     def value_dim(self) -> int:

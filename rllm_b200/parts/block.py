@@ -15,6 +15,8 @@ model's final norm, or a junction, for the last one).  A layer whose spec has no
 has the mixer sublayer only.  Such blocks take the plain path below (no deferred norms, no
 accumulation into the stream by the products).
 
+``post_norm`` (at the end of this file) puts the norms on the sublayers' outputs instead.
+
 A block's interface: ``__init__(layer_spec, runtime)`` builds its parts from the registries;
 ``parts()`` lists them; ``forward(x, pending, ctx, cache) -> pending``.
 
@@ -102,3 +104,61 @@ class PreNormBlock:
         if later is not None:
             return self.ffn.forward(h, ctx, residual=x, then_norm=later)
         return self.ffn.forward(h, ctx, residual=x)
+
+
+@register_part("block", "post_norm")
+class OutputNormBlock:
+    """The norms stand on the sublayers' outputs and the sublayers read the stream itself:
+
+        x += norm_mixer(mixer(x));  x += norm_ffn(ffn(x))        (a spec without a feed-forward: the first only)
+
+    The stream is float32; a product's operand is the stream rounded to the activation type.  The
+    kernel that joins a sublayer's normed output to the stream also writes that rounded copy for the
+    sublayer after it, and leaves it in the pass's scratch for the block that follows; only the
+    first block of a pass makes its own.  Nothing is owed to the stream when the block returns
+    (`pending` is None on both sides)."""
+
+    CAPTURE_SAFE = True
+    TRACEABLE = False
+    DEFERS_NORM = False
+
+    def __init__(self, layer_spec, runtime):
+        self.runtime = runtime
+        self.norm_mixer = build_part("norm", layer_spec.norms["mixer"], runtime)
+        self.mixer = build_part("mixer", layer_spec.mixer, runtime)
+        self.ffn = build_part("ffn", layer_spec.ffn, runtime) if layer_spec.ffn is not None else None
+        self.norm_ffn = build_part("norm", layer_spec.norms["ffn"], runtime) if self.ffn is not None else None
+        self.position = (build_part("position", layer_spec.position, runtime)
+                         if layer_spec.position is not None else None)
+        self.CAPTURE_SAFE = all(getattr(p, "CAPTURE_SAFE", False) for p in self.parts())
+
+    def parts(self):
+        ps = [self.norm_mixer, self.mixer]
+        if self.ffn is not None:
+            ps += [self.norm_ffn, self.ffn]
+        if self.position is not None:
+            ps.append(self.position)
+        return ps
+
+    def _operand(self, x, ctx):
+        """The stream as a product's operand: itself in float32, else its rounded copy."""
+        import torch
+        if self.runtime.is_f32:
+            return x, None
+        key = ("stream_copy", x.data_ptr())
+        h = ctx.scratch.get(key)
+        if h is None:
+            h = ctx.scratch[key] = torch.empty(x.shape, dtype=self.runtime.dtype, device=x.device)
+            ops.rows_act(x, h)                     # a plain conversion
+        return h, h
+
+    def forward(self, x, pending, ctx, cache):
+        if pending is not None:
+            raise ValueError("post_norm: the block before still owes the stream something; it joins its outputs itself")
+        h, copy = self._operand(x, ctx)
+        a = self.mixer.forward(h, ctx, cache, self.position)
+        self.norm_mixer.join(x, a, copy)           # x and its copy are the new stream
+        if self.ffn is not None:
+            f = self.ffn.forward(h, ctx)
+            self.norm_ffn.join(x, f, copy)
+        return None

@@ -88,3 +88,39 @@ class DenseAct(FeedForward):
         act = torch.empty(up.shape, dtype=self.runtime.dtype, device=h.device)
         ops.rows_act(up, act, act=self.activation)
         return ops.linear(act, self.w_down, out_dtype=torch.float32)
+
+
+@register_part("ffn", "clamped_glu")
+class ClampedGLU(FeedForward):
+    """Gated feed-forward with clamped branches:
+
+        g = min(h . Wg^T, limit),  u = clamp(h . Wu^T, -limit, limit)
+        out = (g * sigmoid(alpha * g) * (u + shift)) . Wd^T
+
+    Parameters: hidden_size, intermediate_size, limit (0: no clamp), alpha, shift.  Tensors
+    <prefix>gate, <prefix>up, <prefix>down; gate and up are stacked into one [2F, hidden] matrix."""
+    CAPTURE_SAFE = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.hidden_size = int(params["hidden_size"])
+        self.intermediate_size = int(params["intermediate_size"])
+        self.limit = float(params.get("limit", 0.0) or 0.0)
+        self.alpha = float(params.get("alpha", 1.0))
+        self.shift = float(params.get("shift", 0.0))
+        self.w_gate_up = self.w_down = None
+
+    def expected_tensors(self):
+        F, d, p = self.intermediate_size, self.hidden_size, self.prefix
+        return {p + "gate": ((F, d), "matrix"), p + "up": ((F, d), "matrix"), p + "down": ((d, F), "matrix")}
+
+    def load(self, tensors):
+        p, dt = self.prefix, self.runtime.dtype
+        self.w_gate_up = self._to_device(torch.cat([tensors[p + "gate"].to(dt), tensors[p + "up"].to(dt)], 0))
+        self.w_down = self._to_device(tensors[p + "down"])
+
+    def forward(self, h, ctx=None, residual=None):
+        gu = ops.linear(h, self.w_gate_up, out_dtype=torch.float32)
+        act = torch.empty((h.shape[0], self.intermediate_size), dtype=self.runtime.dtype, device=h.device)
+        ops.glu_clamped(gu, act, self.limit, self.alpha, self.shift)
+        return ops.linear(act, self.w_down, out_dtype=torch.float32)

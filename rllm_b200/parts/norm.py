@@ -5,7 +5,8 @@ directly (no 1 + w), statistics in float32 (AxiomOperator/rllm:
 crates/rllm-cpu/src/lib.rs:241-254; the fusion with the residual add is
 crates/rllm-cuda/kernels/kernels.cu:794-820 and crates/rllm-model/src/qwen3.rs:202-208).
 Parameters: size, eps, optionally `tensor` (the weight's full name).  Tensor: <prefix>weight
-[size], kept in float32.  `delta_scale`: the delta joins the stream multiplied by it.
+[size], kept in float32.  `delta_scale`: the delta joins the stream multiplied by it.  `join(x, y)`: the norm of a sublayer's
+output, x += norm(y) * weight.
 """
 from __future__ import annotations
 
@@ -37,6 +38,12 @@ class RMSNorm(Norm):
         """(weight, eps) for a product kernel that prepares this norm in its epilogue (the division by
         the rms then happens in the product after it: csrc/ops.NormedRows)."""
         return self.weight, self.eps
+
+    def join(self, x, y, copy=None):
+        """x += y / rms(y) * weight: the norm stands on a sublayer's OUTPUT `y` as it joins the float32
+        stream `x` (in place).  `copy`, if given, also takes the new x in its own type (the operand of
+        the next product).  Returns `copy`, or x."""
+        return ops.norm_rows(y, self.weight, self.eps, x=x, add=True, low=copy)
 
     def forward(self, x, delta=None, rows=None, write_x=True, delta_scale=1.0):
         n = x.shape[0] if rows is None else rows.numel()

@@ -78,3 +78,58 @@ class RotaryNeox(Part):
         ops.qkv_norm_rope_store_fused(h, w_qkv, q_norm_w, k_norm_w, self._angles(ctx), cache.slots, q_out, cache.k,
                                       cache.v, H, K, head_dim, cache.block_size, eps, write_kv=cache.write)
         return True
+
+
+@register_part("position", "rotary_scaled")
+class RotaryScaled(Part):
+    """Rotate-half rotary encoding over the first `dims` entries of a head (the rest pass), with
+    optional YaRN-style frequency scaling.
+
+    f_i = base^(-2i / dims) for i < dims/2.  With `scaling` = {factor, original, fast, slow}: let
+    dim(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0),
+    hi = min(ceil(dim(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1); pair
+    i then turns with f_i / factor * ramp_i + f_i * (1 - ramp_i), and cos and sin are multiplied by
+    `mult` = 0.1 ln(factor) + 1.  Frequencies are worked out in double precision on the host and
+    rounded once; angles (position * frequency), cos and sin are float32 on the device.
+
+    Parameters: dims, base, scaling (or None).  No tensors.  The part offers `table()` (the
+    frequencies), `mult` and `angles(ctx)` (cos, sin per token and pair, once per pass); the mixer's
+    own kernel applies them."""
+    CAPTURE_SAFE = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        import math
+        self.dims = int(params["dims"])
+        self.base = float(params["base"])
+        if self.dims <= 0 or self.dims % 2:
+            raise PartError(f"rotary_scaled: dims {self.dims} must be positive and even")
+        half = self.dims // 2
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(half)]
+        self.mult = 1.0
+        sc = params.get("scaling")
+        if sc:
+            factor, original = float(sc["factor"]), float(sc["original"])
+
+            def dim_of(turns):
+                return self.dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+            lo = max(math.floor(dim_of(float(sc["fast"]))), 0)
+            hi = min(math.ceil(dim_of(float(sc["slow"]))), self.dims - 1)
+            for i in range(half):
+                ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+                f[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp)
+            self.mult = 0.1 * math.log(factor) + 1.0
+        self._key = ("rotary_scaled", self.dims, tuple(f))
+        self.freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(runtime.device)
+
+    def table(self):
+        return self.freq
+
+    def angles(self, ctx):
+        """(cos, sin) [n, dims/2, 2] of the step's tokens, shared by the layers with these frequencies."""
+        from ..csrc import ops
+        table = ctx.scratch.get(self._key)
+        if table is None:
+            with ops.untraced():
+                table = ctx.scratch[self._key] = ops.rope_table(ctx.positions, self.freq)
+        return table
