@@ -125,6 +125,28 @@ def qwen3_shape(width: int, layers: int) -> dict:
                 num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=3 * width, vocab_size=32768)
 
 
+def govopel_shape(width: int) -> dict:
+    """A Govopel configuration with layer sizes of a real model of that width: attention through
+    latents (a latent of 512 + 64 entries, heads of 128 + 64 and values of 128), two layers of chunked
+    attention (heads of 128, a quarter as many key/value heads, half of each head rotated with frequency
+    scaling, runs of 1,024 positions, capped scores), attention through latents again; that order twice:
+    eight layer runs, every one with a clamped gated feed-forward of 3 widths."""
+    heads = max(8, width // 128)
+    mlp = {"kind": "dense", "ff": 3 * width, "limit": 7.0}
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512,
+                        "q_rank": min(1536, 3 * width // 4), "rot": {"dims": 64, "base": 10000.0}, "scale": 192 ** -0.5},
+              "mlp": mlp}
+    chunked = {"type": "attention",
+               "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "mask": {"size": 1024},
+                         "rot": {"dims": 64, "base": 500000.0,
+                                 "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}},
+                         "scale": 12.0 / 128, "softcap": 50.0},
+               "mlp": mlp}
+    return {"architecture": "Govopel", "vocab": 32768, "width": width, "layers": [latent, chunked, chunked, latent] * 2,
+            "norm": {"eps": 1e-6}, "logit_softcap": 30.0}
+
+
 def falalix_compare(a):
     """Prefill (one step of 2,048 tokens) and decode (batch 8 behind 2,048-token prompts, replayed
     from CUDA graphs) of Falalix-shaped models beside Qwen3-shaped models of the same width, number
@@ -138,7 +160,8 @@ def falalix_compare(a):
     torch.cuda.set_device(0)
     g = torch.Generator().manual_seed(1)
     widths = {"1k": 1024, "2k": 2048, "4k": 4096}
-    out = {"metric": "Falalix-shaped against Qwen3-shaped models of equal width and depth: prefill tok/s "
+    family = a.workload
+    out = {"metric": f"{family.capitalize()}-shaped against Qwen3-shaped models of equal width and depth: prefill tok/s "
                      "(2,048 tokens, one step) and decode tok/s (batch 8, 2,048-token prompts)",
            "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "dtype": "bf16", "impl": "ours",
            "data": "synthetic: random weights, uniform random token ids", "sizes": {}}
@@ -148,17 +171,19 @@ def falalix_compare(a):
     for size in a.sizes.split(","):
         width = widths[size]
         row = {}
-        for name in ("falalix", "qwen3"):
-            fal = falalix_shape(width)
-            runs = len(fal["layers"]) + (fal["loop"]["stop"] - fal["loop"]["start"]) * (fal["loop"]["times"] - 1)
-            config = config_from_dict(fal if name == "falalix" else qwen3_shape(width, runs))
+        for name in (family, "qwen3"):
+            fal = falalix_shape(width) if family == "falalix" else govopel_shape(width)
+            runs = len(fal["layers"])
+            if fal.get("loop"):
+                runs += (fal["loop"]["stop"] - fal["loop"]["start"]) * (fal["loop"]["times"] - 1)
+            config = config_from_dict(fal if name == family else qwen3_shape(width, runs))
             model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0", generate_on_device=True)
             V = model.spec.vocab_size
             eng = Engine(model, block_size=32, max_tokens=a.batch * (PROMPT + 256), max_requests=a.batch)
             prompts = [torch.randint(0, V, (PROMPT,), generator=g).tolist() for _ in range(a.batch)]
             if a.profile:
                 # one step between cudaProfilerStart/Stop (ncu --profile-from-start off), no benchmark line
-                if name != "falalix":
+                if name != family:
                     continue
                 if a.profile == "prefill":
                     eng.step([StepItem("p", prompts[0], [PROMPT - 1])])
@@ -176,7 +201,7 @@ def falalix_compare(a):
                     eng.step([StepItem(b, [7], [0]) for b in range(a.batch)])
                 torch.cuda.synchronize()
                 torch.cuda.profiler.stop()
-                print(f"profiled one {a.profile} step of the Falalix shape {size}")
+                print(f"profiled one {a.profile} step of the {family} shape {size}")
                 return 0
             times = []
             for rep in range(4):                       # prefill of one prompt in one step; the first loads kernels
@@ -230,12 +255,13 @@ def main():
     ap.add_argument("--ctx", type=int, default=None, help="tokens a request may hold (default: twice the prompt)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "falalix"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "falalix", "govopel"],
                     help="decode: the default line.  serving: --requests prompts of 16..2,048 tokens with 128..512 "
                          "generated tokens each through LLM.generate (continuous batching), one line of its own.  "
                          "falalix: prefill and decode of Falalix-shaped models (--sizes) beside Qwen3-shaped models of "
-                         "equal width, depth and feed-forward, one line of its own")
-    ap.add_argument("--sizes", default="1k,2k,4k", help="falalix: model widths to run (1k, 2k, 4k)")
+                         "equal width, depth and feed-forward, one line of its own.  govopel: the same for "
+                         "Govopel-shaped models")
+    ap.add_argument("--sizes", default="1k,2k,4k", help="falalix, govopel: model widths to run (1k, 2k, 4k)")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--parallel", type=int, default=32, help="serving: requests running at once")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="serving: prompt tokens per step")
@@ -249,7 +275,7 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     a.warmup = max(a.warmup, 3)
-    if a.workload == "falalix":
+    if a.workload in ("falalix", "govopel"):
         return falalix_compare(a)
     PROMPT = a.prompt_len
     CTX = a.ctx if a.ctx is not None else 2 * PROMPT

@@ -46,7 +46,17 @@ struct FlashParams {
     int split_keys;           // 0: no split
     int part_rows;            // rows kept per partial (TT * GH)
     float scale_log2;         // softmax scale * log2(e)
+    int chunk;                // > 0: a token sees only the keys of its own run of `chunk` positions (counted from 0)
+    float cap_in, cap_out;    // capped scores (cap_out > 0): v = cap_out * tanh(s * cap_in), cap_in = scale / cap,
+                              // cap_out = cap * log2(e)
 };
+
+// score -> exponent of the softmax (base 2).  Capped: tanh(x) = 1 - 2 / (e^(2x) + 1), which is exact in
+// both tails and has an absolute error of about 1e-7 (times the cap: far below a bfloat16 key's rounding).
+__device__ __forceinline__ float flash_exponent(const FlashParams& p, float s) {
+    if (p.cap_out > 0.f) return p.cap_out * (1.0f - __fdividef(2.0f, __expf(2.0f * s * p.cap_in) + 1.0f));
+    return s * p.scale_log2;
+}
 
 // A table entry outside the pool is refused: page 0 is read in its place (its keys are masked or
 // not, the step's results are not to be used either way) and the error word says so.
@@ -109,6 +119,7 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     const int nh = min(p.GH, grp - hc * p.GH);
     const int pos_first = p.positions[tok0], pos_last = p.positions[tok0 + nt - 1];
     int lo = p.window > 0 ? max(0, pos_first + 1 - p.window) : 0;
+    if (p.chunk > 0) lo = max(lo, pos_first - pos_first % p.chunk);      // the first token's run starts first
     lo = lo / BN * BN;
     // The kept first keys that lie before the first window tile: [0, sink_end).  Without splits they are
     // extra tiles ahead of the window's; with splits the last split is theirs (and may be empty).  Kept
@@ -131,8 +142,12 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     const int tl0 = R0 / p.GH, hl0 = R0 % p.GH, tl1 = R1 / p.GH, hl1 = R1 % p.GH;
     const bool valid0 = tl0 < nt && hl0 < nh, valid1 = tl1 < nt && hl1 < nh;
     const int pos0 = valid0 ? p.positions[tok0 + tl0] : -1, pos1 = valid1 ? p.positions[tok0 + tl1] : -1;
-    const int first0 = (p.window > 0 && !sink_split) ? max(0, pos0 + 1 - p.window) : 0;
-    const int first1 = (p.window > 0 && !sink_split) ? max(0, pos1 + 1 - p.window) : 0;
+    int first0 = (p.window > 0 && !sink_split) ? max(0, pos0 + 1 - p.window) : 0;
+    int first1 = (p.window > 0 && !sink_split) ? max(0, pos1 + 1 - p.window) : 0;
+    if (p.chunk > 0) {
+        if (pos0 >= 0) first0 = max(first0, pos0 - pos0 % p.chunk);
+        if (pos1 >= 0) first1 = max(first1, pos1 - pos1 % p.chunk);
+    }
     const int hi0 = min(pos0 + 1, ke), hi1 = min(pos1 + 1, ke);
 
     if (kb >= ke) {                                // an empty split: mark it so
@@ -238,7 +253,7 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
         for (int j = 0; j < NT_S; ++j) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                float v = s[j][e] * p.scale_log2;
+                float v = flash_exponent(p, s[j][e]);
                 if (need_mask) {
                     const int key = kt + 8 * j + 2 * t + (e & 1);
                     const bool vis = (e < 2) ? ((key >= f0 || key < keepv) && key < h0)
@@ -365,6 +380,7 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
     const int nh = min(p.GH, grp - hc * p.GH);
     const int pos_first = p.positions[tok0], pos_last = p.positions[tok0 + nt - 1];
     int lo = p.window > 0 ? max(0, pos_first + 1 - p.window) : 0;
+    if (p.chunk > 0) lo = max(lo, pos_first - pos_first % p.chunk);      // the first token's run starts first
     lo = lo / BN * BN;
     // The kept first keys that lie before the first window tile: [0, sink_end).  Without splits they are
     // extra tiles ahead of the window's; with splits the last split is theirs (and may be empty).  Kept
@@ -393,6 +409,7 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
         validc[x] = tlc[x] < nt && hlc[x] < nh;
         const int pos = validc[x] ? p.positions[tok0 + tlc[x]] : -1;
         firstc[x] = (p.window > 0 && !sink_split) ? max(0, pos + 1 - p.window) : 0;
+        if (p.chunk > 0 && pos >= 0) firstc[x] = max(firstc[x], pos - pos % p.chunk);
         hic[x] = min(pos + 1, ke);
     }
     if (kb >= ke) {                                // an empty split: mark it so
@@ -542,7 +559,7 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
         for (int j = 0; j < KB; ++j) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                float v = s[j][e] * p.scale_log2;
+                float v = flash_exponent(p, s[j][e]);
                 if (need_mask) {
                     const int key = kt + 16 * j + g + (e >> 1) * 8;
                     const int x = e & 1;
@@ -726,14 +743,17 @@ static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_split
 // head size other than 64 or 128.
 // keep_first > 0 (with a window): the first keys of a request stay visible behind the window; in mode 1
 // the LAST of the n_splits splits then belongs to them, so the caller counts one split more.
-RLLM_API int rllm_paged_flash_attention_kept(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                             float* part_o, float* part_ml, const int* positions, const int* cu_q,
-                                             const int* block_table, int table_stride, const int* tile_req,
-                                             const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
-                                             float scale, int window, int keep_first, int mode, int TT, int GH,
-                                             int head_chunks, int split_keys, int n_splits, long long n_pages,
-                                             int* err, cudaStream_t stream) {
+// chunk > 0: the chunked mask (runs of `chunk` positions counted from 0; a token sees the keys of its
+// own run up to itself).  softcap > 0: scores go through softcap * tanh(s * scale / softcap).
+RLLM_API int rllm_paged_flash_attention_masked(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                               float* part_o, float* part_ml, const int* positions, const int* cu_q,
+                                               const int* block_table, int table_stride, const int* tile_req,
+                                               const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
+                                               float scale, int window, int keep_first, int mode, int TT, int GH,
+                                               int head_chunks, int split_keys, int n_splits, long long n_pages,
+                                               int* err, int chunk, float softcap, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
+    if (chunk < 0 || softcap < 0.f) return (int)cudaErrorInvalidValue;
     if (keep_first < 0 || (keep_first > 0 && mode == 1 && n_splits < 2)) return (int)cudaErrorInvalidValue;
     const int rows = mode == 0 ? 64 : 16;
     if (K <= 0 || H % K || TT <= 0 || GH <= 0 || TT * GH > rows || head_chunks * GH < H / K || bs <= 0)
@@ -749,9 +769,25 @@ RLLM_API int rllm_paged_flash_attention_kept(const void* q, const void* k_cache,
     p.keep_first = window > 0 ? keep_first : 0;
     p.split_keys = mode == 0 ? 0 : split_keys; p.part_rows = TT * GH;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.chunk = chunk;
+    p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+    p.cap_out = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     if (hd == 128) return launch_flash<128>(p, mode, n_tiles, n_splits, stream);
     if (hd == 64) return launch_flash<64>(p, mode, n_tiles, n_splits, stream);
     return (int)cudaErrorInvalidValue;
+}
+
+RLLM_API int rllm_paged_flash_attention_kept(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                             float* part_o, float* part_ml, const int* positions, const int* cu_q,
+                                             const int* block_table, int table_stride, const int* tile_req,
+                                             const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
+                                             float scale, int window, int keep_first, int mode, int TT, int GH,
+                                             int head_chunks, int split_keys, int n_splits, long long n_pages,
+                                             int* err, cudaStream_t stream) {
+    return rllm_paged_flash_attention_masked(q, k_cache, v_cache, out, part_o, part_ml, positions, cu_q, block_table,
+                                             table_stride, tile_req, tile_tok0, n_tiles, H, K, hd, bs, scale, window,
+                                             keep_first, mode, TT, GH, head_chunks, split_keys, n_splits, n_pages, err,
+                                             0, 0.f, stream);
 }
 
 RLLM_API int rllm_paged_flash_attention(const void* q, const void* k_cache, const void* v_cache, void* out,
@@ -824,3 +860,4 @@ RLLM_API int rllm_paged_flash_decode_static(const void* q, const void* k_cache, 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_paged_flash_attention)
 RLLM_PACKED(rllm_paged_flash_attention_kept)
+RLLM_PACKED(rllm_paged_flash_attention_masked)

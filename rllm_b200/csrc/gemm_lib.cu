@@ -49,6 +49,23 @@ RLLM_API int rllm_gemm_lib(const void* A, const void* W, void* C, int c_dtype, i
     return s == CUBLAS_STATUS_SUCCESS ? 0 : 10000 + (int)s;
 }
 
+// C[m,n] = A[m,k] . B[k,n] with B row-major as it lies (no transpose): probabilities times values.
+RLLM_API int rllm_gemm_lib_nn(const void* A, const void* B, void* C, int c_dtype, int m, int n, int k, int lda,
+                              int ldb, int ldc, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (k <= 0) return (int)cudaErrorInvalidValue;
+    cublasHandle_t h;
+    int st = get_handle(&h);
+    if (st) return st;
+    if (cublasSetStream(h, stream) != CUBLAS_STATUS_SUCCESS) return 10003;
+    const float alpha = 1.f, beta = 0.f;
+    // row-major C = A . B  ==  column-major C^T[n,m] = B^T[n,k] . A^T[k,m], both as they lie
+    cublasStatus_t s = cublasGemmEx(h, CUBLAS_OP_N, CUBLAS_OP_N, n, m, k, &alpha, B, CUDA_R_16BF, ldb, A, CUDA_R_16BF,
+                                    lda, &beta, C, c_dtype == RLLM_F32 ? CUDA_R_32F : CUDA_R_16BF, ldc,
+                                    CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+    return s == CUBLAS_STATUS_SUCCESS ? 0 : 10000 + (int)s;
+}
+
 // A batch of independent products (operand b at A + b * sa, W + b * sw, C + b * sc, in elements)
 // through cublasGemmStridedBatchedEx: the per-head products of attention through latents.
 RLLM_API int rllm_gemm_lib_batched(const void* A, const void* W, void* C, int c_dtype, int m, int n, int k,
@@ -71,3 +88,4 @@ RLLM_API int rllm_gemm_lib_batched(const void* A, const void* W, void* C, int c_
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_gemm_lib)
 RLLM_PACKED(rllm_gemm_lib_batched)
+RLLM_PACKED(rllm_gemm_lib_nn)

@@ -16,6 +16,8 @@
 //   glu_clamped        out = g * sigmoid(alpha * g) * (u + shift), g = min(gate, limit),
 //                      u = clamp(up, -limit, limit).
 //   softcap_rows       x = cap * tanh(x / cap) in place.
+//   masked_softmax_rows  a portion's score rows against its request's keys -> probabilities (causal,
+//                      optionally chunked and capped), for attention written as two library products.
 //
 // Angles come from a table of (cos, sin) per token and pair (rope_table: once per pass).  A slot < 0
 // writes nothing to the cache; a slot beyond the pool sets the error word.
@@ -256,6 +258,58 @@ RLLM_API int rllm_softcap_rows(float* x, long long total, float cap, cudaStream_
                        (size_t)total);
 }
 
+// ------------------------------------------------------------------ masked softmax over score rows
+// Scores S [rows, ld] (float32) of one request's portion against its keys 0 .. n_keys-1: row = token *
+// H + head, the token at position pos0 + token.  P [rows, ld_p] (bfloat16) = softmax over the visible
+// keys j (j <= position; with chunk > 0 also j >= position - position % chunk) of s * scale, capped
+// when softcap > 0; every other column up to n_cols is written as zero.  One block per row.
+__global__ void __launch_bounds__(256)
+masked_softmax_rows_kernel(const float* S, long long ld, bf16* P, long long ld_p, int H, int pos0, int n_cols,
+                           float scale, float softcap, int chunk) {
+    __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t row = blockIdx.x;
+    const int pos = pos0 + (int)(row / H);
+    const int lo = chunk > 0 ? pos - pos % chunk : 0, hi = min(pos + 1, n_cols);
+    const float* s = S + row * ld;
+    bf16* p = P + row * ld_p;
+    float mx = -INFINITY;
+    for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) {
+        float v = s[j] * scale;
+        if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+        mx = fmaxf(mx, v);
+    }
+    mx = block_max(mx, red);
+    float sum = 0.f;
+    for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) {
+        float v = s[j] * scale;
+        if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+        sum += expf(v - mx);
+    }
+    sum = block_sum(sum, red);
+    const float inv = 1.0f / sum;
+    for (int j = threadIdx.x; j < n_cols; j += blockDim.x) {
+        float e = 0.f;
+        if (j >= lo && j < hi) {
+            float v = s[j] * scale;
+            if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+            e = expf(v - mx) * inv;
+        }
+        p[j] = __float2bfloat16_rn(e);
+    }
+}
+
+RLLM_API int rllm_masked_softmax_rows(const float* S, long long ld, void* P, long long ld_p, int rows, int H,
+                                      int pos0, int n_cols, float scale, float softcap, int chunk,
+                                      cudaStream_t stream) {
+    if (rows <= 0 || n_cols <= 0) return 0;
+    if (H <= 0 || pos0 < 0 || ld < n_cols || ld_p < n_cols || chunk < 0) return (int)cudaErrorInvalidValue;
+    return rllm_launch(masked_softmax_rows_kernel, dim3(rows), dim3(256), 0, stream, S, ld, (bf16*)P, ld_p, H, pos0,
+                       n_cols, scale, softcap, chunk);
+}
+
+RLLM_PACKED(rllm_masked_softmax_rows)
 RLLM_PACKED(rllm_norm_rows)
 RLLM_PACKED(rllm_rope_unitnorm_store)
 RLLM_PACKED(rllm_latent_rope_store)

@@ -1313,7 +1313,7 @@ class AttentionPlan:
     which requests take the decode shape (16-row tiles, split keys) and which the prefill shape
     (64-row tiles).  Built once per step on the host and shared by every layer of that geometry."""
 
-    def __init__(self, ctx, H, K, window, device):
+    def __init__(self, ctx, H, K, window, device, chunk=0):
         g = H // K
         self.GHd = min(g, DECODE_ROWS)
         self.chunks_d = -(-g // self.GHd)
@@ -1340,6 +1340,8 @@ class AttentionPlan:
                 span = pos_last + 1
                 if window > 0:
                     span = min(span, window + self.TTd + 30)
+                if chunk > 0:                    # the keys of a run, from its start rounded down likewise
+                    span = min(span, chunk + self.TTd + 30)
                 n_splits = max(n_splits, -(-span // DECODE_SPLIT_KEYS))
         for r in pre:
             for t0 in range(0, ctx.q_lens[r], self.TTp):
@@ -1364,10 +1366,11 @@ class AttentionPlan:
 
 def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0,
                           n_tiles, H, K, hd, block_size, scale, window, mode, TT, GH, head_chunks,
-                          split_keys=DECODE_SPLIT_KEYS, n_splits=1, keep_first=0):
+                          split_keys=DECODE_SPLIT_KEYS, n_splits=1, keep_first=0, chunk=0, softcap=0.0):
     """Tensor-core paged attention; mode 0: prefill shape, mode 1: decode shape with split keys
     (allocates the partials as scratch).  keep_first (with a window): the first keys of a request stay
-    visible; in mode 1 one split more, the last, is theirs.  See attention_flash.cu."""
+    visible; in mode 1 one split more, the last, is theirs.  chunk: the chunked mask (runs of that many
+    positions); softcap: capped scores.  See attention_flash.cu."""
     if keep_first and window and mode == 1:
         n_splits += 1
     _need_cuda(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0)
@@ -1380,12 +1383,13 @@ def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table
         rows = n_tiles * K * head_chunks * n_splits * TT * GH
         part_o = torch.empty(rows * hd, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
-    _check(_lib("attn").rllm_paged_flash_attention_kept(
+    _check(_lib("attn").rllm_paged_flash_attention_masked(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(positions),
         _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req), _ptr(tile_tok0),
         c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale), c_int(window),
         c_int(keep_first if window else 0), c_int(mode), c_int(TT), c_int(GH), c_int(head_chunks), c_int(split_keys),
-        c_int(n_splits), c_longlong(k_cache.shape[0]), _ptr(error_word(q.device)), _stream()),
+        c_int(n_splits), c_longlong(k_cache.shape[0]), _ptr(error_word(q.device)), c_int(chunk), c_float(softcap),
+        _stream()),
         "paged_flash_attention")
     global _launches
     if mode == 1:
@@ -1418,30 +1422,110 @@ def attention_tc(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_re
     return out
 
 
+PRODUCTS_MAX_SCORE_BYTES = 1 << 30      # score rows of one call of the attention written as two products
+
+
+def gemm_lib_nn(a, b, out):
+    """out[m,n] = a[m,k] . b[k,n], b row-major as it lies, through cuBLAS (bfloat16, float32 accumulation)."""
+    _need_cuda(a, b, out)
+    m, k = a.shape
+    n = b.shape[1]
+    assert a.dtype == b.dtype == torch.bfloat16 and b.shape[0] == k and out.shape == (m, n)
+    assert a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1
+    st = _lib("blas").rllm_gemm_lib_nn(_ptr(a), _ptr(b), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k),
+                                       c_int(a.stride(0)), c_int(b.stride(0)), c_int(out.stride(0)), _stream())
+    if st >= 10000:
+        raise KernelError(f"gemm_lib_nn: cuBLAS status {st - 10000} for m={m} n={n} k={k}")
+    _check(st, "gemm_lib_nn", own=False)
+    return out
+
+
+def masked_softmax_rows(scores, probs, H, pos0, n_cols, scale, softcap=0.0, chunk=0):
+    """scores [rows, >= n_cols] float32 (row = token * H + head, the token at position pos0 + token) ->
+    probs [rows, >= n_cols] bfloat16: softmax over the visible keys, zero elsewhere.  See headwise.cu."""
+    _need_cuda(scores, probs)
+    _rows2d(scores, "scores"), _rows2d(probs, "probs")
+    rows = scores.shape[0]
+    assert scores.dtype == torch.float32 and probs.dtype == torch.bfloat16 and probs.shape[0] == rows
+    assert scores.shape[1] >= n_cols and probs.shape[1] >= n_cols
+    _check(core().rllm_masked_softmax_rows(_ptr(scores), c_longlong(scores.stride(0)), _ptr(probs),
+                                           c_longlong(probs.stride(0)), c_int(rows), c_int(H), c_int(pos0),
+                                           c_int(n_cols), c_float(scale), c_float(softcap), c_int(chunk), _stream()),
+           "masked_softmax_rows")
+    return probs
+
+
+def shared_kv_attention(q, cache, out, ctx, block_table, H, hd, hdv, block_size, scale, softcap=0.0):
+    """Causal attention of H query heads over ONE key/value head whose values are the first hdv entries
+    of the key rows (attention through a latent).  q [n, H * hd], cache [pages, 1, block_size, hd], out
+    [n, H * hdv].  bfloat16 portions of more than DECODE_MAX_Q tokens are two library products around a
+    softmax kernel per request: the request's pages gathered into one matrix C [keys, hd], scores =
+    Q C^T for all its (token, head) rows at once (the heads share C, so the product has H times the rows
+    of a head's own), probabilities, then P C[:, :hdv].  Every other row (decode steps, float32) takes
+    the plain kernel."""
+    n = q.shape[0]
+    runs = []            # (first row, rows) of the tokens that take the plain kernel, merged
+    big = []
+    lib_ok = (q.dtype == torch.bfloat16 and hd % 8 == 0 and hdv % 8 == 0 and (H * hd) % 8 == 0
+              and block_size % 8 == 0)
+    at = 0
+    for r in range(ctx.n_requests):
+        k = ctx.q_lens[r]
+        if lib_ok and k > DECODE_MAX_Q:
+            big.append((r, at, k))
+        elif runs and runs[-1][0] + runs[-1][1] == at:
+            runs[-1] = (runs[-1][0], runs[-1][1] + k)
+        else:
+            runs.append((at, k))
+        at += k
+    for a, k in runs:
+        paged_attention_generic(q[a:a + k], cache, cache, out[a:a + k], ctx.positions[a:a + k], ctx.seq_ids[a:a + k],
+                                block_table, H, 1, hd, block_size, scale, 0, 0, hdv, 0, softcap)
+    for r, a, k in big:
+        start, length = ctx.start_pos[r], ctx.start_pos[r] + k
+        n_pages = -(-length // block_size)
+        keys = cache.index_select(0, block_table[r, :n_pages].long()).view(n_pages * block_size, hd)
+        L = n_pages * block_size
+        step = max(1, min(k, PRODUCTS_MAX_SCORE_BYTES // (4 * H * L)))
+        for t0 in range(0, k, step):
+            t1 = min(k, t0 + step)
+            rows = (t1 - t0) * H
+            hi = min(L, -(-(start + t1) // 8) * 8)                # keys beyond the last token of these rows are not needed
+            scores = torch.empty((rows, hi), dtype=torch.float32, device=q.device)
+            gemm_lib(q[a + t0:a + t1].view(rows, hd), keys[:hi], scores)
+            probs = torch.empty((rows, hi), dtype=torch.bfloat16, device=q.device)
+            masked_softmax_rows(scores, probs, H, start + t0, hi, scale, softcap)
+            gemm_lib_nn(probs, keys[:hi, :hdv], out[a + t0:a + t1].view(rows, hdv))
+    return out
+
+
 def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_size, scale, window=0,
                     keep_first=0, v_head_dim=None, chunk=0, softcap=0.0):
     """Attention of the step's tokens over the paged cache; chooses the kernel by element type,
     head size and the shape of the step (`ctx`: the step's StepContext).  float32, head sizes
     other than 64 and 128 and value heads of another size than the key heads take the plain kernel;
-    windows that keep the first keys take the mma.sync kernels, not the tcgen05 one."""
+    windows that keep the first keys, chunked masks and capped scores take the mma.sync kernels, not the
+    tcgen05 one."""
     hdv = hd if not v_head_dim else int(v_head_dim)
     keep_first = keep_first if window else 0
-    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd or chunk or softcap:
+    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd:
         return paged_attention_generic(q, k_cache, v_cache, out, ctx.positions, ctx.seq_ids, block_table,
                                        H, K, hd, block_size, scale, window, keep_first, hdv, chunk, softcap)
-    key = (H // K, window)
+    key = (H // K, window, chunk)
     plan = ctx.plans.get(key)
     if plan is None:
-        plan = ctx.plans[key] = AttentionPlan(ctx, H, K, window, q.device)
-    if plan.n_pre and plan.n_tc and USE_ATTENTION_TC and attention_tc_ok(q, hd, block_size, H, K) and not keep_first:
+        plan = ctx.plans[key] = AttentionPlan(ctx, H, K, window, q.device, chunk)
+    if (plan.n_pre and plan.n_tc and USE_ATTENTION_TC and attention_tc_ok(q, hd, block_size, H, K) and not keep_first
+            and not chunk and not softcap):
         attention_tc(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.t_req, plan.t_tok,
                      plan.n_tc, H, K, hd, block_size, scale, window)
     elif plan.n_pre:
         paged_flash_attention(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.p_req,
                               plan.p_tok, plan.n_pre, H, K, hd, block_size, scale, window, 0, plan.TTp,
-                              plan.GHp, plan.chunks_p, keep_first=keep_first)
+                              plan.GHp, plan.chunks_p, keep_first=keep_first, chunk=chunk, softcap=softcap)
     if plan.n_dec:
         paged_flash_attention(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.d_req,
                               plan.d_tok, plan.n_dec, H, K, hd, block_size, scale, window, 1, plan.TTd,
-                              plan.GHd, plan.chunks_d, DECODE_SPLIT_KEYS, plan.n_splits, keep_first=keep_first)
+                              plan.GHd, plan.chunks_d, DECODE_SPLIT_KEYS, plan.n_splits, keep_first=keep_first,
+                              chunk=chunk, softcap=softcap)
     return out

@@ -87,8 +87,8 @@ class LatentAttention(Mixer):
                               cache.slots, q_att, cache.k, H, dq, r, rank, cache.block_size, self.eps,
                               write_kv=cache.write)
         mixed = torch.empty((n, H * rank), dtype=dt, device=dev)
-        ops.paged_attention(q_att, cache.k, cache.k, mixed, ctx, cache.block_table, H, 1, W, cache.block_size,
-                            self.scale, v_head_dim=rank, softcap=self.softcap)
+        ops.shared_kv_attention(q_att, cache.k, mixed, ctx, cache.block_table, H, W, rank, cache.block_size,
+                                self.scale, softcap=self.softcap)
         a = torch.empty((n, H * self.dv), dtype=dt, device=dev)
         ops.head_linear(mixed.view(n, H, rank), self.w_uv, a.view(n, H, self.dv))
         return ops.linear(a, self.w_o, out_dtype=torch.float32)
