@@ -1,0 +1,294 @@
+// Decode-shape attention of many query heads over ONE key/value head whose values are the leading
+// entries of the key rows (attention through a latent): bf16, mma.sync m16n8k16, float32 softmax.
+//
+// A token's H heads all read the same key rows, so they are the M side of the products: a CTA takes
+// one token, 32 of its heads (two m16 tiles; grid.y walks the head chunks) and one split of SPLIT
+// keys (grid.z), which it walks in tiles of 32 keys:
+//
+//   S[32 heads, 32 keys] = Q[32, W] . C[32 keys, W]^T        4 warps: (m-tile, pair of key n-tiles) each
+//   softmax step over the tile, float32 (running max and sum per head in shared memory)
+//   O[32 heads, V] += P[32, 32] . C[32 keys, :V]             4 warps: a quarter of the V value columns each
+//
+// W = key row length (latent + rotated part), V = value length (the latent).  Q and the key tile lie
+// in shared memory with rows padded by 16 bytes, so that the eight 16-byte rows of every ldmatrix
+// fall into eight different bank groups without a swizzle.  Keys beyond the token's position are
+// loaded as zeros and masked.  Every split writes its unnormalized O, max and sum; a second kernel
+// merges the splits of a (token, head) in split order.  The split size is a constant, so a token's
+// result does not depend on the batch around it.
+//
+// Needs W % 16 == 0, V % 64 == 0, V <= 512, V <= W.  Other sizes, float32 and prompt portions take
+// other kernels (ops.shared_kv_attention).
+#include "common.cuh"
+#include <math.h>
+
+#define LAT_HEADS 32        // heads per CTA
+#define LAT_TILE 32         // keys per tile
+#define LAT_PAD 8           // bf16 elements of padding per shared-memory row
+#define LAT_MAX_NT 16       // n8 tiles of value columns per warp (V / 4 / 8)
+
+__device__ __forceinline__ uint32_t lat_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void lat_cp16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void lat_cp_wait_all() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+}
+__device__ __forceinline__ void lat_ldsm(uint32_t a, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void lat_ldsm_t(uint32_t a, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void lat_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct LatentParams {
+    const bf16* q;            // [n, H, W]
+    const bf16* cache;        // [pages, 1, bs, W]
+    float* part_o;            // [n, chunks, splits, LAT_HEADS, V]
+    float* part_ml;           // [n, chunks, splits, LAT_HEADS, 2]
+    const int* positions;     // [n]
+    const int* seq_ids;       // [n]
+    const int* block_table;   // [R, table_stride]
+    int table_stride, n_pages;
+    int* err;
+    int H, W, V, bs, split;
+    float scale, softcap;
+};
+
+__global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int LD = p.W + LAT_PAD;                                   // elements per padded row
+    bf16* Qs = reinterpret_cast<bf16*>(smem);                       // [32][LD]
+    bf16* Ks = Qs + LAT_HEADS * LD;                                 // [32][LD]
+    float* Ss = reinterpret_cast<float*>(Ks + LAT_TILE * LD);       // [32][33]
+    bf16* Ps = reinterpret_cast<bf16*>(Ss + LAT_HEADS * (LAT_TILE + 1));   // [32][32 + 8]
+    float* m_s = reinterpret_cast<float*>(Ps + LAT_HEADS * (LAT_TILE + LAT_PAD));   // [32] running max
+    float* l_s = m_s + LAT_HEADS;                                   // [32] running sum
+    float* a_s = l_s + LAT_HEADS;                                   // [32] rescale of the tile
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int tok = blockIdx.x, hc = blockIdx.y, z = blockIdx.z;
+    const int head0 = hc * LAT_HEADS;
+    const size_t part = ((size_t)tok * gridDim.y + hc) * gridDim.z + z;
+    const int pos = p.positions[tok];
+    const int kb = z * p.split, ke = min(pos + 1, kb + p.split);
+    pdl_wait();
+    if (kb >= ke) {                                                 // an empty split
+        if (tid < LAT_HEADS) {
+            p.part_ml[(part * LAT_HEADS + tid) * 2] = -INFINITY;
+            p.part_ml[(part * LAT_HEADS + tid) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    const int* table = p.block_table + (size_t)p.seq_ids[tok] * p.table_stride;
+    const int chunks = p.W / 8;                                     // 16-byte pieces of a row
+    // queries of this chunk of heads; rows beyond H are zero
+    for (int i = tid; i < LAT_HEADS * chunks; i += 128) {
+        const int r = i / chunks, c = i - r * chunks;
+        const bool live = head0 + r < p.H;
+        const bf16* src = p.q + ((size_t)tok * p.H + (live ? head0 + r : 0)) * p.W + c * 8;
+        lat_cp16(lat_smem(Qs + r * LD + c * 8), src, live ? 16 : 0);
+    }
+    if (tid < LAT_HEADS) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
+    float acc[2][LAT_MAX_NT][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int j = 0; j < LAT_MAX_NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[mt][j][e] = 0.f;
+    const int nt_w = p.V / 32;                                      // n8 tiles of this warp: V / 4 columns
+    const int col0 = warp * (p.V / 4);
+    // ldmatrix lane addresses: A-like (rows r0 + (mi & 1) * 8 + r, columns + (mi >> 1) * 8) and
+    // B-like for the keys as n (rows (mi >> 1) * 8 + r, columns + (mi & 1) * 8)
+    const int mi = lane >> 3, r8 = lane & 7;
+    const int a_row = (mi & 1) * 8 + r8, a_col = (mi >> 1) * 8;
+    const int b_row = (mi >> 1) * 8 + r8, b_col = (mi & 1) * 8;
+
+    for (int kt = kb; kt < ke; kt += LAT_TILE) {
+        // ---- the key tile: rows kt .. kt + 31, zeros beyond ke
+        for (int i = tid; i < LAT_TILE * chunks; i += 128) {
+            const int r = i / chunks, c = i - r * chunks;
+            const int key = kt + r;
+            const bool live = key < ke;
+            int page = live ? table[key / p.bs] : 0;
+            if ((unsigned)page >= (unsigned)p.n_pages) {
+                if (p.err) atomicExch(p.err, RLLM_ERR_PAGE);
+                page = 0;
+            }
+            const bf16* src = p.cache + ((size_t)page * p.bs + (live ? key % p.bs : 0)) * p.W + c * 8;
+            lat_cp16(lat_smem(Ks + r * LD + c * 8), src, live ? 16 : 0);
+        }
+        lat_cp_wait_all();
+        __syncthreads();
+        // ---- S = Q K^T: this warp's m-tile (warp & 1) and keys (warp >> 1) * 16 .. + 15
+        {
+            const int mt = warp & 1, n0 = (warp >> 1) * 16;
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            const uint32_t qa = lat_smem(Qs + (mt * 16 + a_row) * LD + a_col);
+            const uint32_t ka = lat_smem(Ks + (n0 + b_row) * LD + b_col);
+            for (int k0 = 0; k0 < p.W; k0 += 16) {
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                lat_ldsm(qa + k0 * 2, a0, a1, a2, a3);
+                lat_ldsm(ka + k0 * 2, b0, b1, b2, b3);
+                lat_mma(s[0], a0, a1, a2, a3, b0, b1);
+                lat_mma(s[1], a0, a1, a2, a3, b2, b3);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int row = mt * 16 + g + (e >> 1) * 8, col = n0 + j * 8 + 2 * t4 + (e & 1);
+                    float v = s[j][e] * p.scale;
+                    if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
+                    Ss[row * (LAT_TILE + 1) + col] = (kt + col < ke) ? v : -INFINITY;
+                }
+        }
+        __syncthreads();
+        // ---- softmax step: warp w owns heads 8w .. 8w + 7, a lane per key
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int row = warp * 8 + i;
+            const float v = Ss[row * (LAT_TILE + 1) + lane];
+            const float m_old = m_s[row];
+            const float m_new = fmaxf(m_old, warp_max(v));            // the tile's first key is always live
+            const float e = expf(v - m_new);                           // exp(-inf) = 0
+            const float sum = warp_sum(e);
+            Ps[row * (LAT_TILE + LAT_PAD) + lane] = __float2bfloat16_rn(e);
+            __syncwarp();
+            if (lane == 0) {
+                const float alpha = expf(m_old - m_new);               // 0 at the first tile
+                a_s[row] = alpha;
+                l_s[row] = l_s[row] * alpha + sum;
+                m_s[row] = m_new;
+            }
+        }
+        __syncthreads();
+        // ---- O = O * alpha + P V over this warp's value columns
+        {
+            float al[2][2];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) { al[mt][0] = a_s[mt * 16 + g]; al[mt][1] = a_s[mt * 16 + g + 8]; }
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int j = 0; j < LAT_MAX_NT; ++j) {
+                    acc[mt][j][0] *= al[mt][0]; acc[mt][j][1] *= al[mt][0];
+                    acc[mt][j][2] *= al[mt][1]; acc[mt][j][3] *= al[mt][1];
+                }
+#pragma unroll
+            for (int kk = 0; kk < LAT_TILE / 16; ++kk) {
+                uint32_t pa[2][4];
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+                    lat_ldsm(lat_smem(Ps + (mt * 16 + a_row) * (LAT_TILE + LAT_PAD) + kk * 16 + a_col), pa[mt][0],
+                             pa[mt][1], pa[mt][2], pa[mt][3]);
+                // V as the B operand (k = key, n = column): transposed 8x8 pieces of the key tile;
+                // matrices: (keys 0-7, cols 0-7), (keys 8-15, cols 0-7), (keys 0-7, cols 8-15), (keys 8-15, cols 8-15)
+                const uint32_t va = lat_smem(Ks + (kk * 16 + a_row) * LD + col0 + a_col);
+#pragma unroll
+                for (int jp = 0; jp < LAT_MAX_NT / 2; ++jp) {
+                    if (2 * jp < nt_w) {
+                        uint32_t b0, b1, b2, b3;
+                        lat_ldsm_t(va + jp * 32, b0, b1, b2, b3);
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt) {
+                            lat_mma(acc[mt][2 * jp], pa[mt][0], pa[mt][1], pa[mt][2], pa[mt][3], b0, b1);
+                            lat_mma(acc[mt][2 * jp + 1], pa[mt][0], pa[mt][1], pa[mt][2], pa[mt][3], b2, b3);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();                                            // the tile, S and P may be overwritten
+    }
+    pdl_launch_dependents();
+    // ---- this split's partial results
+    float* po = p.part_o + part * LAT_HEADS * p.V;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int j = 0; j < LAT_MAX_NT; ++j)
+            if (j < nt_w) {
+                const int c = col0 + j * 8 + 2 * t4;
+                *reinterpret_cast<float2*>(po + (size_t)(mt * 16 + g) * p.V + c) = make_float2(acc[mt][j][0], acc[mt][j][1]);
+                *reinterpret_cast<float2*>(po + (size_t)(mt * 16 + g + 8) * p.V + c) = make_float2(acc[mt][j][2], acc[mt][j][3]);
+            }
+    if (tid < LAT_HEADS) {
+        p.part_ml[(part * LAT_HEADS + tid) * 2] = m_s[tid];
+        p.part_ml[(part * LAT_HEADS + tid) * 2 + 1] = l_s[tid];
+    }
+}
+
+// out[tok, head, :] = sum_z o_z exp(m_z - m) / sum_z l_z exp(m_z - m), splits in order.  Grid (token, head).
+__global__ void __launch_bounds__(128)
+latent_combine_kernel(const float* part_o, const float* part_ml, bf16* out, int H, int V, int chunks, int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tok = blockIdx.x, head = blockIdx.y;
+    const int hc = head / LAT_HEADS, r = head % LAT_HEADS;
+    const size_t base = ((size_t)tok * chunks + hc) * splits;
+    float m = -INFINITY;
+    for (int z = 0; z < splits; ++z) m = fmaxf(m, part_ml[((base + z) * LAT_HEADS + r) * 2]);
+    float l = 0.f;
+    for (int z = 0; z < splits; ++z) {
+        const float mz = part_ml[((base + z) * LAT_HEADS + r) * 2];
+        if (mz != -INFINITY) l += part_ml[((base + z) * LAT_HEADS + r) * 2 + 1] * expf(mz - m);
+    }
+    const float inv = 1.0f / l;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+        float o = 0.f;
+        for (int z = 0; z < splits; ++z) {
+            const float mz = part_ml[((base + z) * LAT_HEADS + r) * 2];
+            if (mz != -INFINITY) o += part_o[((base + z) * LAT_HEADS + r) * V + c] * expf(mz - m);
+        }
+        out[((size_t)tok * H + head) * V + c] = __float2bfloat16_rn(o * inv);
+    }
+}
+
+// Shared memory of the attention kernel for key rows of W elements.
+static size_t latent_smem(int W) {
+    return (size_t)(LAT_HEADS + LAT_TILE) * (W + LAT_PAD) * 2 + (size_t)LAT_HEADS * (LAT_TILE + 1) * 4 +
+           (size_t)LAT_HEADS * (LAT_TILE + LAT_PAD) * 2 + 3 * LAT_HEADS * 4;
+}
+
+// q [n, H * W], cache [pages, 1, bs, W], out [n, H * V] (all bfloat16); part_o needs n * chunks * n_splits
+// * 32 * V floats, part_ml the same with 2 in place of V (chunks = ceil(H / 32)); n_splits * split_keys
+// must cover the longest context; split_keys a multiple of 32.
+RLLM_API int rllm_latent_decode_attention(const void* q, const void* cache, void* out, float* part_o, float* part_ml,
+                                          const int* positions, const int* seq_ids, const int* block_table,
+                                          int table_stride, int n, int H, int W, int V, int bs, float scale,
+                                          float softcap, int split_keys, int n_splits, long long n_pages, int* err,
+                                          cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (H <= 0 || W % 16 || V % 64 || V <= 0 || V > 8 * LAT_MAX_NT * 4 || V > W || bs <= 0 || split_keys <= 0 ||
+        split_keys % LAT_TILE || n_splits <= 0 || n_splits > 65535 || !part_o || !part_ml || softcap < 0.f)
+        return (int)cudaErrorInvalidValue;
+    const size_t smem = latent_smem(W);
+    if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(latent_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    LatentParams p;
+    p.q = (const bf16*)q; p.cache = (const bf16*)cache; p.part_o = part_o; p.part_ml = part_ml;
+    p.positions = positions; p.seq_ids = seq_ids; p.block_table = block_table; p.table_stride = table_stride;
+    p.n_pages = (int)(n_pages > 0x7fffffffLL ? 0x7fffffffLL : n_pages); p.err = err;
+    p.H = H; p.W = W; p.V = V; p.bs = bs; p.split = split_keys; p.scale = scale; p.softcap = softcap;
+    const int chunks = (H + LAT_HEADS - 1) / LAT_HEADS;
+    int st = rllm_launch(latent_decode_kernel, dim3(n, chunks, n_splits), dim3(128), smem, stream, p);
+    if (st) return st;
+    return rllm_launch(latent_combine_kernel, dim3(n, H), dim3(128), 0, stream, (const float*)part_o,
+                       (const float*)part_ml, (bf16*)out, H, V, chunks, n_splits);
+}
+
+RLLM_PACKED(rllm_latent_decode_attention)

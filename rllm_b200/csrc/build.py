@@ -36,6 +36,7 @@ LIBRARIES = {
     "blas": (["gemm_lib.cu"], ["-lcublas"]),
     "fast": (["skinny_gemm.cu"], []),
     "attn": (["attention_flash.cu"], []),
+    "attn_latent": (["attention_latent.cu"], []),
     "tc": (["gemm_tc.cu"], []),
     "tc2": (["gemm_tc2.cu"], []),
     "stream": (["gemv_stream.cu"], []),

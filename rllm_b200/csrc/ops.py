@@ -1455,14 +1455,48 @@ def masked_softmax_rows(scores, probs, H, pos0, n_cols, scale, softcap=0.0, chun
     return probs
 
 
+LATENT_SPLIT_KEYS = 128        # keys per split of the latent decode kernel: a constant, as DECODE_SPLIT_KEYS
+
+
+def latent_decode_ok(q, hd, hdv) -> bool:
+    return q.dtype == torch.bfloat16 and hd % 16 == 0 and hdv % 64 == 0 and 0 < hdv <= 512 and hdv <= hd and hd <= 1536
+
+
+def latent_decode_attention(q, cache, out, positions, seq_ids, block_table, H, hd, hdv, block_size, scale, softcap,
+                            max_ctx_len):
+    """The decode shape of attention over one shared key/value head on the tensor cores (split keys,
+    partials as scratch, merged by a second kernel); see attention_latent.cu."""
+    _need_cuda(q, cache, out, positions, seq_ids, block_table)
+    _need_contig(q=q, cache=cache, out=out, positions=positions, seq_ids=seq_ids)
+    n = q.shape[0]
+    assert q.shape == (n, H * hd) and out.shape == (n, H * hdv) and cache.shape[1:] == (1, block_size, hd)
+    assert q.dtype == cache.dtype == out.dtype == torch.bfloat16 and block_table.stride(1) == 1
+    if not latent_decode_ok(q, hd, hdv):
+        raise KernelError("latent_decode_attention takes bfloat16, key rows of a multiple of 16 entries up to 1536 and "
+                          "values of a multiple of 64 entries up to 512")
+    n_splits = max(1, -(-int(max_ctx_len) // LATENT_SPLIT_KEYS))
+    rows = n * (-(-H // 32)) * n_splits * 32
+    part_o = torch.empty(rows * hdv, dtype=torch.float32, device=q.device)
+    part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
+    _check(_lib("attn_latent").rllm_latent_decode_attention(
+        _ptr(q), _ptr(cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(positions), _ptr(seq_ids), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(n), c_int(H), c_int(hd), c_int(hdv), c_int(block_size), c_float(scale),
+        c_float(softcap), c_int(LATENT_SPLIT_KEYS), c_int(n_splits), c_longlong(cache.shape[0]),
+        _ptr(error_word(q.device)), _stream()), "latent_decode_attention")
+    global _launches
+    _launches += 1                             # the merge kernel
+    return out
+
+
 def shared_kv_attention(q, cache, out, ctx, block_table, H, hd, hdv, block_size, scale, softcap=0.0):
     """Causal attention of H query heads over ONE key/value head whose values are the first hdv entries
     of the key rows (attention through a latent).  q [n, H * hd], cache [pages, 1, block_size, hd], out
     [n, H * hdv].  bfloat16 portions of more than DECODE_MAX_Q tokens are two library products around a
     softmax kernel per request: the request's pages gathered into one matrix C [keys, hd], scores =
     Q C^T for all its (token, head) rows at once (the heads share C, so the product has H times the rows
-    of a head's own), probabilities, then P C[:, :hdv].  Every other row (decode steps, float32) takes
-    the plain kernel."""
+    of a head's own), probabilities, then P C[:, :hdv].  The other rows (decode steps, short portions)
+    take the tensor-core decode kernel of attention_latent.cu where the sizes allow it; float32 and odd
+    sizes take the plain kernel."""
     n = q.shape[0]
     runs = []            # (first row, rows) of the tokens that take the plain kernel, merged
     big = []
@@ -1479,8 +1513,12 @@ def shared_kv_attention(q, cache, out, ctx, block_table, H, hd, hdv, block_size,
             runs.append((at, k))
         at += k
     for a, k in runs:
-        paged_attention_generic(q[a:a + k], cache, cache, out[a:a + k], ctx.positions[a:a + k], ctx.seq_ids[a:a + k],
-                                block_table, H, 1, hd, block_size, scale, 0, 0, hdv, 0, softcap)
+        if latent_decode_ok(q, hd, hdv):
+            latent_decode_attention(q[a:a + k], cache, out[a:a + k], ctx.positions[a:a + k], ctx.seq_ids[a:a + k],
+                                    block_table, H, hd, hdv, block_size, scale, softcap, ctx.max_ctx_len)
+        else:
+            paged_attention_generic(q[a:a + k], cache, cache, out[a:a + k], ctx.positions[a:a + k],
+                                    ctx.seq_ids[a:a + k], block_table, H, 1, hd, block_size, scale, 0, 0, hdv, 0, softcap)
     for r, a, k in big:
         start, length = ctx.start_pos[r], ctx.start_pos[r] + k
         n_pages = -(-length // block_size)

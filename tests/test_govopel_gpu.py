@@ -204,6 +204,36 @@ def test_plain_attention_kernel_chunk_cap_and_values_in_keys(dtype):
         assert torch.allclose(got, want, atol=1e-5 if dtype == torch.float32 else 3e-2)
 
 
+@pytest.mark.parametrize("H,W,V,cap", [(40, 144, 128, 0.0), (8, 576, 512, 20.0), (3, 80, 64, 0.0)])
+def test_latent_decode_kernel_against_the_plain_kernel(H, W, V, cap):
+    """The tensor-core decode kernel of attention over one shared key/value head (head chunks that are
+    not full, several splits, contexts that end inside a tile, a split and a page; scrambled pages)
+    gives what the plain kernel gives from the same cache."""
+    from rllm_b200.csrc import ops
+    bs, lens = 16, [1, 33, 128, 129, 300, 517]
+    g = torch.Generator().manual_seed(6)
+    n_pages = sum(-(-L // bs) for L in lens)
+    order = torch.randperm(n_pages + 3, generator=g).tolist()
+    cache = torch.randn(n_pages + 3, 1, bs, W, generator=g).to(DEV, torch.bfloat16)
+    table = torch.zeros((len(lens), -(-max(lens) // bs)), dtype=torch.int32)
+    for r, L in enumerate(lens):
+        for b in range(-(-L // bs)):
+            table[r, b] = order.pop()
+    # two tokens of the longest request, one of each other
+    seq = torch.tensor([0, 1, 2, 3, 4, 5, 5], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([0, 32, 127, 128, 299, 515, 516], dtype=torch.int32, device=DEV)
+    q = torch.randn(7, H * W, generator=g).to(DEV, torch.bfloat16)
+    want = torch.empty((7, H * V), dtype=torch.bfloat16, device=DEV)
+    got = torch.zeros_like(want)
+    scale = 1.0 / math.sqrt(W)
+    ops.paged_attention_generic(q, cache, cache, want, pos, seq, table.to(DEV), H, 1, W, bs, scale, v_head_dim=V,
+                                softcap=cap)
+    ops.latent_decode_attention(q, cache, got, pos, seq, table.to(DEV), H, W, V, bs, scale, cap, max(lens))
+    ops.check_device_errors(DEV)
+    assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2), float((got.float() - want.float()).abs().max())
+    assert torch.equal(got[0].view(H, V), cache[table[0, 0], 0, 0, :V].expand(H, V))       # one key: the value itself
+
+
 # ---------------------------------------------------------------- each configuration, each way of cutting
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
