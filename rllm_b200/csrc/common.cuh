@@ -68,6 +68,18 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return red[32];
 }
 
+// The gated activation behind a feed-forward's first product, with its constants:
+// out = g' * sigmoid(alpha * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit)
+// (limit 0: no clamp).  SwiGLU is {0, 1, 0}, for which the arithmetic below is the plain form's.
+struct GluForm { float limit, alpha, shift; };
+__device__ __forceinline__ float glu_apply(const GluForm f, float g, float u) {
+    if (f.limit > 0.f) {
+        g = fminf(g, f.limit);
+        u = fminf(fmaxf(u, -f.limit), f.limit);
+    }
+    return g / (1.0f + __expf(-f.alpha * g)) * (u + f.shift);
+}
+
 // Programmatic dependent launch (griddepcontrol): `pdl_wait` blocks until the kernels this one
 // depends on have completed and their writes are visible (a no-op for an ordinary launch);
 // `pdl_launch_dependents` lets the next kernel of the stream begin to launch early.  A kernel

@@ -68,7 +68,7 @@ template <> __device__ __forceinline__ void store_row32<bf16>(bf16* dst, const f
 template <int BN, int EPI, typename TC, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TC* __restrict__ C,
-               int ldc, int M, int N, int K, int up_row_offset, int* __restrict__ err) {
+               int ldc, int M, int N, int K, int up_row_offset, int* __restrict__ err, const GluForm glu) {
     constexpr int A_BYTES = TC_BM * TC_BK * 2;
     constexpr int B_BYTES = BN * TC_BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -200,7 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const float g = __uint_as_float(r[j]);
-                        v[j] = g / (1.0f + __expf(-g)) * __uint_as_float(u[j]);
+                        v[j] = glu_apply(glu, g, __uint_as_float(u[j]));
                     }
                 } else {
                     tmem_ld_wait();
@@ -257,7 +257,7 @@ static int make_tmap(CUtensorMap* map, const void* base, int rows, int cols, int
 
 template <int BN, int EPI, typename TC, int STAGES>
 static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int ldc, int M, int N, int K, int up,
-                     int* err, cudaStream_t stream) {
+                     int* err, cudaStream_t stream, const GluForm glu = GluForm{0.f, 1.f, 0.f}) {
     constexpr int BN_OUT = (EPI == TC_EPI_SWIGLU) ? BN / 2 : BN;
     constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
     auto kern = gemm_tc_kernel<BN, EPI, TC, STAGES>;
@@ -276,7 +276,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int 
     }
     const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN_OUT - 1) / BN_OUT);
     dim3 grid(tiles < n_sm ? tiles : n_sm);
-    return rllm_launch(kern, grid, dim3(TC_THREADS), smem, stream, ta, tb, (TC*)C, ldc, M, N, K, up, err);
+    return rllm_launch(kern, grid, dim3(TC_THREADS), smem, stream, ta, tb, (TC*)C, ldc, M, N, K, up, err, glu);
 }
 
 // C[M,N] (+)= A[M,K] . B[N,K]^T on the tcgen05 tensor cores.  epilogue 0 store, 1 accumulate into a
@@ -284,8 +284,11 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int 
 // silu(gate) * up).  A, B bfloat16 row-major with 16-byte aligned bases and lda, ldb multiples of 8;
 // K a multiple of 8.  `err` is a device int that receives a code if a bounded wait ran out.
 // Returns 0, a cudaError_t, 30000 + CUresult of the tensor-map encoder, or cudaErrorInvalidValue.
-RLLM_API int rllm_gemm_tc(const void* A, const void* B, void* C, int c_dtype, int M, int N, int K, int lda, int ldb,
-                          int ldc, int epilogue, int up_row_offset, int* err, cudaStream_t stream) {
+// glu_*: the constants of the gated epilogue (GluForm in common.cuh); rllm_gemm_tc is SwiGLU's {0, 1, 0}.
+RLLM_API int rllm_gemm_tc_glu(const void* A, const void* B, void* C, int c_dtype, int M, int N, int K, int lda, int ldb,
+                              int ldc, int epilogue, int up_row_offset, float glu_limit, float glu_alpha,
+                              float glu_shift, int* err, cudaStream_t stream) {
+    const GluForm glu = GluForm{glu_limit, glu_alpha, glu_shift};
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || !err)
         return (int)cudaErrorInvalidValue;
@@ -304,10 +307,15 @@ RLLM_API int rllm_gemm_tc(const void* A, const void* B, void* C, int c_dtype, in
         return launch_tc<256, TC_EPI_ACCUM, float, 4>(ta, tb, C, ldc, M, N, K, 0, err, stream);
     } else if (epilogue == TC_EPI_SWIGLU) {
         return c_dtype == RLLM_F32
-                   ? launch_tc<256, TC_EPI_SWIGLU, float, 4>(ta, tb, C, ldc, M, N, K, up_row_offset, err, stream)
-                   : launch_tc<256, TC_EPI_SWIGLU, bf16, 4>(ta, tb, C, ldc, M, N, K, up_row_offset, err, stream);
+                   ? launch_tc<256, TC_EPI_SWIGLU, float, 4>(ta, tb, C, ldc, M, N, K, up_row_offset, err, stream, glu)
+                   : launch_tc<256, TC_EPI_SWIGLU, bf16, 4>(ta, tb, C, ldc, M, N, K, up_row_offset, err, stream, glu);
     }
     return (int)cudaErrorInvalidValue;
+}
+
+RLLM_API int rllm_gemm_tc(const void* A, const void* B, void* C, int c_dtype, int M, int N, int K, int lda, int ldb,
+                          int ldc, int epilogue, int up_row_offset, int* err, cudaStream_t stream) {
+    return rllm_gemm_tc_glu(A, B, C, c_dtype, M, N, K, lda, ldb, ldc, epilogue, up_row_offset, 0.f, 1.f, 0.f, err, stream);
 }
 
 // =====================================================================================================
@@ -774,4 +782,5 @@ TC_DEFINE_WAIT_CONTROLS(rllm_tc)
 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_gemm_tc)
+RLLM_PACKED(rllm_gemm_tc_glu)
 RLLM_PACKED(rllm_gemm_tc_swap)

@@ -161,7 +161,8 @@ __device__ __forceinline__ void t2_item(int item, int head, int tail_log2, int& 
 template <int EPI, typename TC, int STAGES, int HD = 128>
 __global__ void __launch_bounds__(T2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ T2Maps maps, TC* __restrict__ C, int ldc, int M, int N, int K,
-                int up_row_offset, int* __restrict__ err, int tail_tiles, int tail_log2, const T2Qkv qk) {
+                int up_row_offset, int* __restrict__ err, int tail_tiles, int tail_log2, const T2Qkv qk,
+                const GluForm glu) {
     constexpr int BN_OUT = (EPI == T2_EPI_SWIGLU) ? T2_BN / 2 : T2_BN;      // output columns per tile
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -375,7 +376,7 @@ gemm_tc2_kernel(const __grid_constant__ T2Maps maps, TC* __restrict__ C, int ldc
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const float g = __uint_as_float(r[j]);
-                        v[j] = g / (1.0f + __expf(-g)) * __uint_as_float(u[j]);
+                        v[j] = glu_apply(glu, g, __uint_as_float(u[j]));
                     }
                 } else {
                     tmem_ld_wait();
@@ -432,7 +433,7 @@ static int t2_make_tmap(CUtensorMap* map, const void* base, int rows, int cols, 
 
 template <int EPI, typename TC, int STAGES, int HD = 128>
 static int launch_tc2(const T2Maps& maps, void* C, int ldc, int M, int N, int K, int up, int* err, cudaStream_t stream,
-                      const T2Qkv& qk = T2Qkv()) {
+                      const T2Qkv& qk = T2Qkv(), const GluForm glu = GluForm{0.f, 1.f, 0.f}) {
     constexpr int BN_OUT = (EPI == T2_EPI_SWIGLU) ? T2_BN / 2 : T2_BN;
     constexpr size_t smem = (size_t)STAGES * T2_STAGE_BYTES + 1024;
     auto kern = gemm_tc2_kernel<EPI, TC, STAGES, HD>;
@@ -461,13 +462,16 @@ static int launch_tc2(const T2Maps& maps, void* C, int ldc, int M, int N, int K,
     const int items = tiles - tail_tiles + (tail_tiles << tail_log2);
     const int pairs = items < all_pairs ? items : all_pairs;
     return rllm_launch_clusters(kern, dim3(2 * pairs), dim3(T2_THREADS), smem, stream, dim3(2, 1, 1), maps, (TC*)C, ldc,
-                                M, N, K, up, err, tail_tiles, tail_log2, qk);
+                                M, N, K, up, err, tail_tiles, tail_log2, qk, glu);
 }
 
 // C[M,N] (+)= A[M,K] . B[N,K]^T with two SMs per 256 x 256 tile.  Arguments, epilogues and return
 // values as rllm_gemm_tc (gemm_tc.cu).
-RLLM_API int rllm_gemm_tc2(const void* A, const void* B, void* C, int c_dtype, int M, int N, int K, int lda, int ldb,
-                           int ldc, int epilogue, int up_row_offset, int* err, cudaStream_t stream) {
+// glu_*: the constants of the gated epilogue (GluForm in common.cuh); rllm_gemm_tc2 is SwiGLU's {0, 1, 0}.
+RLLM_API int rllm_gemm_tc2_glu(const void* A, const void* B, void* C, int c_dtype, int M, int N, int K, int lda,
+                               int ldb, int ldc, int epilogue, int up_row_offset, float glu_limit, float glu_alpha,
+                               float glu_shift, int* err, cudaStream_t stream) {
+    const GluForm glu = GluForm{glu_limit, glu_alpha, glu_shift};
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || !err)
         return (int)cudaErrorInvalidValue;
@@ -487,10 +491,15 @@ RLLM_API int rllm_gemm_tc2(const void* A, const void* B, void* C, int c_dtype, i
         return launch_tc2<T2_EPI_ACCUM, float, 3>(maps, C, ldc, M, N, K, 0, err, stream);
     } else if (epilogue == T2_EPI_SWIGLU) {
         return c_dtype == RLLM_F32
-                   ? launch_tc2<T2_EPI_SWIGLU, float, 3>(maps, C, ldc, M, N, K, up_row_offset, err, stream)
-                   : launch_tc2<T2_EPI_SWIGLU, bf16, 3>(maps, C, ldc, M, N, K, up_row_offset, err, stream);
+                   ? launch_tc2<T2_EPI_SWIGLU, float, 3>(maps, C, ldc, M, N, K, up_row_offset, err, stream, T2Qkv(), glu)
+                   : launch_tc2<T2_EPI_SWIGLU, bf16, 3>(maps, C, ldc, M, N, K, up_row_offset, err, stream, T2Qkv(), glu);
     }
     return (int)cudaErrorInvalidValue;
+}
+
+RLLM_API int rllm_gemm_tc2(const void* A, const void* B, void* C, int c_dtype, int M, int N, int K, int lda, int ldb,
+                           int ldc, int epilogue, int up_row_offset, int* err, cudaStream_t stream) {
+    return rllm_gemm_tc2_glu(A, B, C, c_dtype, M, N, K, lda, ldb, ldc, epilogue, up_row_offset, 0.f, 1.f, 0.f, err, stream);
 }
 
 // The fused q/k/v projection of a prompt step with the q/k norm, the rotary encoding and the cache
@@ -527,4 +536,5 @@ TC_DEFINE_WAIT_CONTROLS(rllm_tc2)
 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_gemm_tc2)
+RLLM_PACKED(rllm_gemm_tc2_glu)
 RLLM_PACKED(rllm_qkv_tc2)

@@ -263,9 +263,13 @@ RLLM_API int rllm_softcap_rows(float* x, long long total, float cap, cudaStream_
 // H + head, the token at position pos0 + token.  P [rows, ld_p] (bfloat16) = softmax over the visible
 // keys j (j <= position; with chunk > 0 also j >= position - position % chunk) of s * scale, capped
 // when softcap > 0; every other column up to n_cols is written as zero.  One block per row.
+// STAGED: the row's visible scores are read once into shared memory (n_cols floats) and the other two passes
+// run from there; rows too long for that read global memory three times.
+template <bool STAGED>
 __global__ void __launch_bounds__(256)
 masked_softmax_rows_kernel(const float* S, long long ld, bf16* P, long long ld_p, int H, int pos0, int n_cols,
                            float scale, float softcap, int chunk) {
+    extern __shared__ float staged[];
     __shared__ float red[33];
     pdl_wait();
     pdl_launch_dependents();
@@ -278,23 +282,34 @@ masked_softmax_rows_kernel(const float* S, long long ld, bf16* P, long long ld_p
     for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) {
         float v = s[j] * scale;
         if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+        if (STAGED) staged[j] = v;
         mx = fmaxf(mx, v);
     }
     mx = block_max(mx, red);
     float sum = 0.f;
     for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) {
-        float v = s[j] * scale;
-        if (softcap > 0.f) v = softcap * tanhf(v / softcap);
-        sum += expf(v - mx);
+        float v;
+        if (STAGED) {
+            v = staged[j] = expf(staged[j] - mx);
+        } else {
+            v = s[j] * scale;
+            if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+            v = expf(v - mx);
+        }
+        sum += v;
     }
     sum = block_sum(sum, red);
     const float inv = 1.0f / sum;
     for (int j = threadIdx.x; j < n_cols; j += blockDim.x) {
         float e = 0.f;
         if (j >= lo && j < hi) {
-            float v = s[j] * scale;
-            if (softcap > 0.f) v = softcap * tanhf(v / softcap);
-            e = expf(v - mx) * inv;
+            if (STAGED) {
+                e = staged[j] * inv;
+            } else {
+                float v = s[j] * scale;
+                if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+                e = expf(v - mx) * inv;
+            }
         }
         p[j] = __float2bfloat16_rn(e);
     }
@@ -305,8 +320,11 @@ RLLM_API int rllm_masked_softmax_rows(const float* S, long long ld, void* P, lon
                                       cudaStream_t stream) {
     if (rows <= 0 || n_cols <= 0) return 0;
     if (H <= 0 || pos0 < 0 || ld < n_cols || ld_p < n_cols || chunk < 0) return (int)cudaErrorInvalidValue;
-    return rllm_launch(masked_softmax_rows_kernel, dim3(rows), dim3(256), 0, stream, S, ld, (bf16*)P, ld_p, H, pos0,
-                       n_cols, scale, softcap, chunk);
+    if (n_cols <= 11264)                     // 44 KB: within the shared memory every launch may have
+        return rllm_launch(masked_softmax_rows_kernel<true>, dim3(rows), dim3(256), (size_t)n_cols * sizeof(float),
+                           stream, S, ld, (bf16*)P, ld_p, H, pos0, n_cols, scale, softcap, chunk);
+    return rllm_launch(masked_softmax_rows_kernel<false>, dim3(rows), dim3(256), 0, stream, S, ld, (bf16*)P, ld_p, H,
+                       pos0, n_cols, scale, softcap, chunk);
 }
 
 RLLM_PACKED(rllm_masked_softmax_rows)

@@ -918,9 +918,10 @@ def _tc_ok(a, w, _meta=False) -> bool:
             and (_meta or a.data_ptr() % 16 == 0) and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
+def gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, glu=None):
     """out (+)= a . w^T on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory).
-    epilogue as for skinny_gemm.  See gemm_tc.cu."""
+    epilogue as for skinny_gemm; glu = (limit, alpha, shift): the gated epilogue's constants (None:
+    SwiGLU).  See gemm_tc.cu."""
     _need_cuda(a, w, out)
     if not _tc_ok(a, w):
         raise KernelError("gemm_tc needs bfloat16 operands, k a multiple of 8 and 16-byte aligned rows")
@@ -931,17 +932,18 @@ def gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
         assert w.shape[0] >= up_row_offset + n
     else:
         assert w.shape[0] == n
-    st = _lib("tc").rllm_gemm_tc(
+    limit, alpha, shift = glu or (0.0, 1.0, 0.0)
+    st = _lib("tc").rllm_gemm_tc_glu(
         _ptr(a), _ptr(w), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
-        c_int(w.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset),
-        _ptr(error_word(a.device)), _stream())
+        c_int(w.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset), c_float(limit),
+        c_float(alpha), c_float(shift), _ptr(error_word(a.device)), _stream())
     if st >= 30000:
         raise KernelError(f"gemm_tc: tensor map encoding failed (CUresult {st - 30000}) for m={m} n={n} k={k}")
     _check(st, "gemm_tc")
     return out
 
 
-def gemm_tc2(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
+def gemm_tc2(a, w, out, epilogue=EPI_STORE, up_row_offset=0, glu=None):
     """out (+)= a . w^T on the tcgen05 tensor cores with two SMs per 256 x 256 tile
     (tcgen05.mma.cta_group::2; each CTA of the pair stages half of the operands).  Arguments as
     gemm_tc.  See gemm_tc2.cu."""
@@ -955,10 +957,11 @@ def gemm_tc2(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
         assert w.shape[0] >= up_row_offset + n
     else:
         assert w.shape[0] == n
-    st = _lib("tc2").rllm_gemm_tc2(
+    limit, alpha, shift = glu or (0.0, 1.0, 0.0)
+    st = _lib("tc2").rllm_gemm_tc2_glu(
         _ptr(a), _ptr(w), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
-        c_int(w.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset),
-        _ptr(error_word(a.device)), _stream())
+        c_int(w.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset), c_float(limit),
+        c_float(alpha), c_float(shift), _ptr(error_word(a.device)), _stream())
     if st >= 30000:
         raise KernelError(f"gemm_tc2: tensor map encoding failed (CUresult {st - 30000}) for m={m} n={n} k={k}")
     _check(st, "gemm_tc2")
@@ -1277,13 +1280,21 @@ def _prefer_tc2(m: int, n_col_tiles: int, n_sm: int = 148) -> bool:
 USE_TC2 = True
 
 
-def gate_up_swiglu(h, w_gate_up, out):
+def gate_up_swiglu(h, w_gate_up, out, glu=None):
     """out[m, F] = silu(h . Wg^T) * (h . Wu^T) with w_gate_up = [Wg; Wu] stacked ([2F, k]).
     bfloat16: one kernel (the weight-streaming kernel up to 64 rows, the tcgen05 kernel above);
-    float32 and odd shapes: a product followed by the activation kernel."""
+    float32 and odd shapes: a product followed by the activation kernel.
+    glu = (limit, alpha, shift): another gated form, g sigmoid(alpha g) (u + shift) with g = min(gate,
+    limit), u = clamp(up, -limit, limit); the tcgen05 kernels take it in their epilogue, fewer rows and
+    the other shapes a product followed by the activation kernel."""
     m = h.shape[0]
     F = out.shape[1]
     rows = h.xw if isinstance(h, NormedRows) else h
+    if glu is not None:
+        if not _skinny_ok(rows, w_gate_up) and _tc_ok(h, w_gate_up) and out.data_ptr() % 16 == 0:
+            many = gemm_tc2 if _prefer_tc2(m, -(-F // 128), sm_count(h.device)) else gemm_tc
+            return many(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F, glu=glu)
+        return glu_clamped(linear(h, w_gate_up, out_dtype=torch.float32), out, *glu)
     if _skinny_ok(rows, w_gate_up):
         if _prefer_stream(rows, w_gate_up, 2 * F, swiglu=True):
             return gemv_stream(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)

@@ -120,7 +120,6 @@ class ClampedGLU(FeedForward):
         self.w_down = self._to_device(tensors[p + "down"])
 
     def forward(self, h, ctx=None, residual=None):
-        gu = ops.linear(h, self.w_gate_up, out_dtype=torch.float32)
         act = torch.empty((h.shape[0], self.intermediate_size), dtype=self.runtime.dtype, device=h.device)
-        ops.glu_clamped(gu, act, self.limit, self.alpha, self.shift)
+        ops.gate_up_swiglu(h, self.w_gate_up, act, glu=(self.limit, self.alpha, self.shift))
         return ops.linear(act, self.w_down, out_dtype=torch.float32)
