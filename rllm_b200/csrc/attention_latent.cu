@@ -11,7 +11,8 @@
 //
 // W = key row length (latent + rotated part), V = value length (the latent).  Q and the key tile lie
 // in shared memory with rows padded by 16 bytes, so that the eight 16-byte rows of every ldmatrix
-// fall into eight different bank groups without a swizzle.  Keys beyond the token's position are
+// fall into eight different bank groups without a swizzle; the next key tile is on its way (cp.async,
+// second buffer) while the current one is worked on.  Keys beyond the token's position are
 // loaded as zeros and masked.  Every split writes its unnormalized O, max and sum; a second kernel
 // merges the splits of a (token, head) in split order.  The split size is a constant, so a token's
 // result does not depend on the batch around it.
@@ -29,9 +30,6 @@
 __device__ __forceinline__ uint32_t lat_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void lat_cp16(uint32_t dst, const void* src, int bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
-}
-__device__ __forceinline__ void lat_cp_wait_all() {
-    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
 __device__ __forceinline__ void lat_ldsm(uint32_t a, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -67,8 +65,8 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
     extern __shared__ __align__(128) unsigned char smem[];
     const int LD = p.W + LAT_PAD;                                   // elements per padded row
     bf16* Qs = reinterpret_cast<bf16*>(smem);                       // [32][LD]
-    bf16* Ks = Qs + LAT_HEADS * LD;                                 // [32][LD]
-    float* Ss = reinterpret_cast<float*>(Ks + LAT_TILE * LD);       // [32][33]
+    bf16* Kbuf = Qs + LAT_HEADS * LD;                               // two key tiles [32][LD]: one in use, one on its way
+    float* Ss = reinterpret_cast<float*>(Kbuf + 2 * LAT_TILE * LD); // [32][33]
     bf16* Ps = reinterpret_cast<bf16*>(Ss + LAT_HEADS * (LAT_TILE + 1));   // [32][32 + 8]
     float* m_s = reinterpret_cast<float*>(Ps + LAT_HEADS * (LAT_TILE + LAT_PAD));   // [32] running max
     float* l_s = m_s + LAT_HEADS;                                   // [32] running sum
@@ -112,11 +110,11 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
     const int a_row = (mi & 1) * 8 + r8, a_col = (mi >> 1) * 8;
     const int b_row = (mi >> 1) * 8 + r8, b_col = (mi & 1) * 8;
 
-    for (int kt = kb; kt < ke; kt += LAT_TILE) {
-        // ---- the key tile: rows kt .. kt + 31, zeros beyond ke
+    // a key tile on its way: rows first .. first + 31 of the request, zeros beyond ke; one cp.async group
+    auto fetch_tile = [&](bf16* dst, int first) {
         for (int i = tid; i < LAT_TILE * chunks; i += 128) {
             const int r = i / chunks, c = i - r * chunks;
-            const int key = kt + r;
+            const int key = first + r;
             const bool live = key < ke;
             int page = live ? table[key / p.bs] : 0;
             if ((unsigned)page >= (unsigned)p.n_pages) {
@@ -124,9 +122,20 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
                 page = 0;
             }
             const bf16* src = p.cache + ((size_t)page * p.bs + (live ? key % p.bs : 0)) * p.W + c * 8;
-            lat_cp16(lat_smem(Ks + r * LD + c * 8), src, live ? 16 : 0);
+            lat_cp16(lat_smem(dst + r * LD + c * 8), src, live ? 16 : 0);
         }
-        lat_cp_wait_all();
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    fetch_tile(Kbuf, kb);                                           // with the queries in the same group
+    int cur = 0;
+    for (int kt = kb; kt < ke; kt += LAT_TILE, cur ^= 1) {
+        bf16* Ks = Kbuf + cur * LAT_TILE * LD;
+        if (kt + LAT_TILE < ke) {                                   // the next tile travels while this one is worked on
+            fetch_tile(Kbuf + (cur ^ 1) * LAT_TILE * LD, kt + LAT_TILE);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
         __syncthreads();
         // ---- S = Q K^T: this warp's m-tile (warp & 1) and keys (warp >> 1) * 16 .. + 15
         {
@@ -227,9 +236,11 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
     }
 }
 
-// out[tok, head, :] = sum_z o_z exp(m_z - m) / sum_z l_z exp(m_z - m), splits in order.  Grid (token, head).
+// out[tok, head, :] = sum_z o_z exp(m_z - m) / sum_z l_z exp(m_z - m), splits in order.  Grid (token, head);
+// the splits' weights exp(m_z - m) / l are worked out once, into shared memory (splits floats).
 __global__ void __launch_bounds__(128)
 latent_combine_kernel(const float* part_o, const float* part_ml, bf16* out, int H, int V, int chunks, int splits) {
+    extern __shared__ float wz[];
     pdl_wait();
     pdl_launch_dependents();
     const int tok = blockIdx.x, head = blockIdx.y;
@@ -243,19 +254,22 @@ latent_combine_kernel(const float* part_o, const float* part_ml, bf16* out, int 
         if (mz != -INFINITY) l += part_ml[((base + z) * LAT_HEADS + r) * 2 + 1] * expf(mz - m);
     }
     const float inv = 1.0f / l;
+    for (int z = threadIdx.x; z < splits; z += blockDim.x) {
+        const float mz = part_ml[((base + z) * LAT_HEADS + r) * 2];
+        wz[z] = mz != -INFINITY ? expf(mz - m) * inv : 0.f;
+    }
+    __syncthreads();
     for (int c = threadIdx.x; c < V; c += blockDim.x) {
         float o = 0.f;
-        for (int z = 0; z < splits; ++z) {
-            const float mz = part_ml[((base + z) * LAT_HEADS + r) * 2];
-            if (mz != -INFINITY) o += part_o[((base + z) * LAT_HEADS + r) * V + c] * expf(mz - m);
-        }
-        out[((size_t)tok * H + head) * V + c] = __float2bfloat16_rn(o * inv);
+        for (int z = 0; z < splits; ++z)
+            if (wz[z] != 0.f) o += part_o[((base + z) * LAT_HEADS + r) * V + c] * wz[z];
+        out[((size_t)tok * H + head) * V + c] = __float2bfloat16_rn(o);
     }
 }
 
 // Shared memory of the attention kernel for key rows of W elements.
 static size_t latent_smem(int W) {
-    return (size_t)(LAT_HEADS + LAT_TILE) * (W + LAT_PAD) * 2 + (size_t)LAT_HEADS * (LAT_TILE + 1) * 4 +
+    return (size_t)(LAT_HEADS + 2 * LAT_TILE) * (W + LAT_PAD) * 2 + (size_t)LAT_HEADS * (LAT_TILE + 1) * 4 +
            (size_t)LAT_HEADS * (LAT_TILE + LAT_PAD) * 2 + 3 * LAT_HEADS * 4;
 }
 
@@ -269,7 +283,7 @@ RLLM_API int rllm_latent_decode_attention(const void* q, const void* cache, void
                                           cudaStream_t stream) {
     if (n <= 0) return 0;
     if (H <= 0 || W % 16 || V % 64 || V <= 0 || V > 8 * LAT_MAX_NT * 4 || V > W || bs <= 0 || split_keys <= 0 ||
-        split_keys % LAT_TILE || n_splits <= 0 || n_splits > 65535 || !part_o || !part_ml || softcap < 0.f)
+        split_keys % LAT_TILE || n_splits <= 0 || n_splits > 8192 || !part_o || !part_ml || softcap < 0.f)
         return (int)cudaErrorInvalidValue;
     const size_t smem = latent_smem(W);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
@@ -287,7 +301,7 @@ RLLM_API int rllm_latent_decode_attention(const void* q, const void* cache, void
     const int chunks = (H + LAT_HEADS - 1) / LAT_HEADS;
     int st = rllm_launch(latent_decode_kernel, dim3(n, chunks, n_splits), dim3(128), smem, stream, p);
     if (st) return st;
-    return rllm_launch(latent_combine_kernel, dim3(n, H), dim3(128), 0, stream, (const float*)part_o,
+    return rllm_launch(latent_combine_kernel, dim3(n, H), dim3(128), (size_t)n_splits * sizeof(float), stream, (const float*)part_o,
                        (const float*)part_ml, (bf16*)out, H, V, chunks, n_splits);
 }
 

@@ -1434,6 +1434,7 @@ def attention_tc(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_re
 
 
 PRODUCTS_MAX_SCORE_BYTES = 1 << 30      # score rows of one call of the attention written as two products
+PRODUCTS_BLOCK_TOKENS = 512             # tokens of a portion whose score rows are one product
 
 
 def gemm_lib_nn(a, b, out):
@@ -1470,7 +1471,7 @@ LATENT_SPLIT_KEYS = 128        # keys per split of the latent decode kernel: a c
 
 
 def latent_decode_ok(q, hd, hdv) -> bool:
-    return q.dtype == torch.bfloat16 and hd % 16 == 0 and hdv % 64 == 0 and 0 < hdv <= 512 and hdv <= hd and hd <= 1536
+    return q.dtype == torch.bfloat16 and hd % 16 == 0 and hdv % 64 == 0 and 0 < hdv <= 512 and hdv <= hd and hd <= 1152
 
 
 def latent_decode_attention(q, cache, out, positions, seq_ids, block_table, H, hd, hdv, block_size, scale, softcap,
@@ -1483,7 +1484,7 @@ def latent_decode_attention(q, cache, out, positions, seq_ids, block_table, H, h
     assert q.shape == (n, H * hd) and out.shape == (n, H * hdv) and cache.shape[1:] == (1, block_size, hd)
     assert q.dtype == cache.dtype == out.dtype == torch.bfloat16 and block_table.stride(1) == 1
     if not latent_decode_ok(q, hd, hdv):
-        raise KernelError("latent_decode_attention takes bfloat16, key rows of a multiple of 16 entries up to 1536 and "
+        raise KernelError("latent_decode_attention takes bfloat16, key rows of a multiple of 16 entries up to 1152 and "
                           "values of a multiple of 64 entries up to 512")
     n_splits = max(1, -(-int(max_ctx_len) // LATENT_SPLIT_KEYS))
     rows = n * (-(-H // 32)) * n_splits * 32
@@ -1535,7 +1536,9 @@ def shared_kv_attention(q, cache, out, ctx, block_table, H, hd, hdv, block_size,
         n_pages = -(-length // block_size)
         keys = cache.index_select(0, block_table[r, :n_pages].long()).view(n_pages * block_size, hd)
         L = n_pages * block_size
-        step = max(1, min(k, PRODUCTS_MAX_SCORE_BYTES // (4 * H * L)))
+        # blocks of tokens: a block's products stop at its last token's key, so shorter blocks skip more of the
+        # masked upper triangle (a third of the work at four blocks) for three more launches each
+        step = max(1, min(k, PRODUCTS_BLOCK_TOKENS, PRODUCTS_MAX_SCORE_BYTES // (4 * H * L)))
         for t0 in range(0, k, step):
             t1 = min(k, t0 + step)
             rows = (t1 - t0) * H
