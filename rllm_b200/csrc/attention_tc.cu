@@ -68,6 +68,9 @@ struct AttnTcParams {
     int n_pages;                // a table entry outside [0, n_pages) is refused (page 0 is read, RLLM_ERR_PAGE)
     float scale_log2;
     int* err;
+    int chunk;                  // > 0: a token sees only the keys of its own run of `chunk` positions (counted from 0)
+    float cap_in, cap_pre;      // capped scores (cap_pre > 0): s <- cap_pre * tanh(s * cap_in) before the scale, with
+                                // cap_in = scale / cap and cap_pre = cap / scale
 };
 
 // K-major, 128-byte swizzle (Q, K, P): see smem_desc_sw128.  MN-major (V: dims contiguous):
@@ -120,6 +123,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int head0 = kvh * p.g;
     const int pos_first = p.positions[tok0], pos_last = p.positions[tok0 + nt - 1];
     int kb = p.window > 0 ? max(0, pos_first + 1 - p.window) : 0;
+    if (p.chunk > 0) kb = max(kb, pos_first - pos_first % p.chunk);       // the first token's run starts first
     kb = kb / AT_BN * AT_BN;
     const int n_kt = (pos_last + 1 - kb + AT_BN - 1) / AT_BN;      // >= 1
 
@@ -298,7 +302,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int tl = r / p.g, hl = r % p.g;
         const bool valid = tl < nt;
         const int pos_r = valid ? p.positions[tok0 + tl] : -1;
-        const int first_r = p.window > 0 ? max(0, pos_r + 1 - p.window) : 0;
+        int first_r = p.window > 0 ? max(0, pos_r + 1 - p.window) : 0;
+        if (p.chunk > 0 && pos_r >= 0) first_r = max(first_r, pos_r - pos_r % p.chunk);
         const int bar_mine = 1 + wg * 4 + quarter;           // arrived at by this warp, waited for by its partner
         const int bar_partner = 1 + (1 - wg) * 4 + quarter;
         const int b = wg;
@@ -327,6 +332,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 for (int c = 0; c < AT_BN; ++c) sv[c] = __uint_as_float(rr[c >> 5][c & 31]);
                 tc_fence_before();
                 mbar_arrive(&s_empty[b]);
+                if (p.cap_pre > 0.f) {
+                    // capped scores: tanh(x) = 1 - 2 / (e^(2x) + 1), two MUFU a score, exact in both tails
+                    const float two_in_log2 = 2.0f * 1.4426950408889634f * p.cap_in;
+#pragma unroll
+                    for (int c = 0; c < AT_BN; ++c)
+                        sv[c] = p.cap_pre * (1.0f - __fdividef(2.0f, ex2_approx(sv[c] * two_in_log2) + 1.0f));
+                }
                 // The maximum is taken over the raw scores (the scale is positive) and the scale goes
                 // into the exponent's multiply-add: one FFMA and one MUFU per score.
                 const bool need_mask = (kt + AT_BN > pos_r + 1) || (kt < first_r);
@@ -475,11 +487,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
 // q, out [n, H, 128] bfloat16; caches [pages, K, bs, 128] bfloat16; tiles of TT = 128 / (H / K) tokens.
 // Returns cudaErrorInvalidValue for shapes outside the limits named at the top of this file.
-RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v_cache, void* out, int n_tokens,
-                               long long n_pages, const int* positions, const int* cu_q, const int* block_table,
-                               int table_stride, const int* tile_req, const int* tile_tok0, int n_tiles, int H, int K,
-                               int hd, int bs, float scale, int window, int* err, cudaStream_t stream) {
+// chunk > 0: the chunked mask; softcap > 0: scores go through softcap * tanh(s * scale / softcap).
+RLLM_API int rllm_attention_tc_masked(const void* q, const void* k_cache, const void* v_cache, void* out, int n_tokens,
+                                      long long n_pages, const int* positions, const int* cu_q, const int* block_table,
+                                      int table_stride, const int* tile_req, const int* tile_tok0, int n_tiles, int H,
+                                      int K, int hd, int bs, float scale, int window, int chunk, float softcap, int* err,
+                                      cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
+    if (chunk < 0 || softcap < 0.f || !(scale > 0.f)) return (int)cudaErrorInvalidValue;
     if (hd != AT_HD || K <= 0 || H % K || bs < 8 || bs > 128 || (bs & (bs - 1)) || !err) return (int)cudaErrorInvalidValue;
     const int g = H / K;
     if (g > 128 || 128 % g) return (int)cudaErrorInvalidValue;
@@ -508,6 +523,9 @@ RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v
     p.tile_tok0 = tile_tok0; p.table_stride = table_stride; p.H = H; p.K = K; p.bs = bs; p.window = window; p.TT = TT;
     p.g = g; p.n_tiles = n_tiles; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
     p.n_pages = (int)(n_pages > 0x7fffffffLL ? 0x7fffffffLL : n_pages);
+    p.chunk = chunk;
+    p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+    p.cap_pre = softcap > 0.f ? softcap / scale : 0.f;
     constexpr int smem = (1 + AT_KS + AT_VS) * AT_TILE_BYTES + 1024;
     static bool attr_set = false;
     if (!attr_set) {
@@ -518,7 +536,17 @@ RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v
     return rllm_launch(attention_tc_kernel, dim3(n_tiles, K), dim3(AT_THREADS), smem, stream, tq, tk, tv, p);
 }
 
+RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v_cache, void* out, int n_tokens,
+                               long long n_pages, const int* positions, const int* cu_q, const int* block_table,
+                               int table_stride, const int* tile_req, const int* tile_tok0, int n_tiles, int H, int K,
+                               int hd, int bs, float scale, int window, int* err, cudaStream_t stream) {
+    return rllm_attention_tc_masked(q, k_cache, v_cache, out, n_tokens, n_pages, positions, cu_q, block_table,
+                                    table_stride, tile_req, tile_tok0, n_tiles, H, K, hd, bs, scale, window, 0, 0.f, err,
+                                    stream);
+}
+
 TC_DEFINE_WAIT_CONTROLS(rllm_attn_tc)
 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_attention_tc)
+RLLM_PACKED(rllm_attention_tc_masked)

@@ -1415,18 +1415,18 @@ def attention_tc_ok(q, hd, block_size, H, K) -> bool:
 
 
 def attention_tc(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0, n_tiles, H, K, hd,
-                 block_size, scale, window):
+                 block_size, scale, window, chunk=0, softcap=0.0):
     """Prefill attention on the tcgen05 tensor cores (S and O in tensor memory); see attention_tc.cu."""
     _need_cuda(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0)
     _need_contig(q=q, k_cache=k_cache, v_cache=v_cache, out=out)
     if not attention_tc_ok(q, hd, block_size, H, K):
         raise KernelError("attention_tc takes bfloat16, head size 128, a power-of-two page size from 8 to 128 and "
                           "a number of query heads per key/value head that divides 128")
-    st = _lib("attn_tc").rllm_attention_tc(
+    st = _lib("attn_tc").rllm_attention_tc_masked(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), c_int(q.shape[0]), c_longlong(k_cache.shape[0]),
         _ptr(positions), _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req),
         _ptr(tile_tok0), c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale),
-        c_int(window), _ptr(error_word(q.device)), _stream())
+        c_int(window), c_int(chunk), c_float(softcap), _ptr(error_word(q.device)), _stream())
     if st >= 30000:
         raise KernelError(f"attention_tc: tensor map encoding failed (CUresult {st - 30000})")
     _check(st, "attention_tc")
@@ -1556,8 +1556,7 @@ def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_
     """Attention of the step's tokens over the paged cache; chooses the kernel by element type,
     head size and the shape of the step (`ctx`: the step's StepContext).  float32, head sizes
     other than 64 and 128 and value heads of another size than the key heads take the plain kernel;
-    windows that keep the first keys, chunked masks and capped scores take the mma.sync kernels, not the
-    tcgen05 one."""
+    windows that keep the first keys take the mma.sync kernels, not the tcgen05 one."""
     hdv = hd if not v_head_dim else int(v_head_dim)
     keep_first = keep_first if window else 0
     if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS or hdv != hd:
@@ -1567,10 +1566,9 @@ def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_
     plan = ctx.plans.get(key)
     if plan is None:
         plan = ctx.plans[key] = AttentionPlan(ctx, H, K, window, q.device, chunk)
-    if (plan.n_pre and plan.n_tc and USE_ATTENTION_TC and attention_tc_ok(q, hd, block_size, H, K) and not keep_first
-            and not chunk and not softcap):
+    if plan.n_pre and plan.n_tc and USE_ATTENTION_TC and attention_tc_ok(q, hd, block_size, H, K) and not keep_first:
         attention_tc(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.t_req, plan.t_tok,
-                     plan.n_tc, H, K, hd, block_size, scale, window)
+                     plan.n_tc, H, K, hd, block_size, scale, window, chunk, softcap)
     elif plan.n_pre:
         paged_flash_attention(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.p_req,
                               plan.p_tok, plan.n_pre, H, K, hd, block_size, scale, window, 0, plan.TTp,
