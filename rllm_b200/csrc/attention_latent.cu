@@ -5,9 +5,12 @@
 // one token, 32 of its heads (two m16 tiles; grid.y walks the head chunks) and one split of SPLIT
 // keys (grid.z), which it walks in tiles of 32 keys:
 //
-//   S[32 heads, 32 keys] = Q[32, W] . C[32 keys, W]^T        4 warps: (m-tile, pair of key n-tiles) each
-//   softmax step over the tile, float32 (running max and sum per head in shared memory)
-//   O[32 heads, V] += P[32, 32] . C[32 keys, :V]             4 warps: a quarter of the V value columns each
+//   S[16 heads, 32 keys] = Q[16, W] . C[32 keys, W]^T        per warp: its m-tile against the whole key tile
+//   softmax step over the tile, float32, in registers (a head's scores lie in the four lanes of a quad)
+//   O[16 heads, V/2] += P[16, 32] . C[32 keys, half of :V]   per warp: its m-tile, one half of the value columns
+//
+// The two warps of an m-tile compute the same scores (the products are not the limit), so that P never
+// leaves the registers and a tile costs one block barrier, for its buffer.
 //
 // W = key row length (latent + rotated part), V = value length (the latent).  Q and the key tile lie
 // in shared memory with rows padded by 16 bytes, so that the eight 16-byte rows of every ldmatrix
@@ -25,7 +28,7 @@
 #define LAT_HEADS 32        // heads per CTA
 #define LAT_TILE 32         // keys per tile
 #define LAT_PAD 8           // bf16 elements of padding per shared-memory row
-#define LAT_MAX_NT 16       // n8 tiles of value columns per warp (V / 4 / 8)
+#define LAT_MAX_NT 32       // n8 tiles of value columns per warp (V / 2 / 8)
 
 __device__ __forceinline__ uint32_t lat_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void lat_cp16(uint32_t dst, const void* src, int bytes) {
@@ -61,16 +64,16 @@ struct LatentParams {
     float scale, softcap;
 };
 
+__device__ __forceinline__ uint32_t lat_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
 __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int LD = p.W + LAT_PAD;                                   // elements per padded row
     bf16* Qs = reinterpret_cast<bf16*>(smem);                       // [32][LD]
     bf16* Kbuf = Qs + LAT_HEADS * LD;                               // two key tiles [32][LD]: one in use, one on its way
-    float* Ss = reinterpret_cast<float*>(Kbuf + 2 * LAT_TILE * LD); // [32][33]
-    bf16* Ps = reinterpret_cast<bf16*>(Ss + LAT_HEADS * (LAT_TILE + 1));   // [32][32 + 8]
-    float* m_s = reinterpret_cast<float*>(Ps + LAT_HEADS * (LAT_TILE + LAT_PAD));   // [32] running max
-    float* l_s = m_s + LAT_HEADS;                                   // [32] running sum
-    float* a_s = l_s + LAT_HEADS;                                   // [32] rescale of the tile
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int tok = blockIdx.x, hc = blockIdx.y, z = blockIdx.z;
     const int head0 = hc * LAT_HEADS;
@@ -94,18 +97,20 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
         const bf16* src = p.q + ((size_t)tok * p.H + (live ? head0 + r : 0)) * p.W + c * 8;
         lat_cp16(lat_smem(Qs + r * LD + c * 8), src, live ? 16 : 0);
     }
-    if (tid < LAT_HEADS) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
-    float acc[2][LAT_MAX_NT][4];
+    // This warp: the 16 heads of m-tile `mt` against ALL keys of a tile (so a head's scores, its softmax
+    // step and its P fragments stay in this warp's registers: the two warps of an m-tile compute the same
+    // scores), and for P . V the half `ch` of the value columns.
+    const int mt = warp & 1, ch = warp >> 1;
+    const int nt_w = p.V / 16;                                      // n8 tiles of this warp: V / 2 columns
+    const int col0 = ch * (p.V / 2);
+    float acc[LAT_MAX_NT][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int j = 0; j < LAT_MAX_NT; ++j)
 #pragma unroll
-        for (int j = 0; j < LAT_MAX_NT; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[mt][j][e] = 0.f;
-    const int nt_w = p.V / 32;                                      // n8 tiles of this warp: V / 4 columns
-    const int col0 = warp * (p.V / 4);
-    // ldmatrix lane addresses: A-like (rows r0 + (mi & 1) * 8 + r, columns + (mi >> 1) * 8) and
-    // B-like for the keys as n (rows (mi >> 1) * 8 + r, columns + (mi & 1) * 8)
+        for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};      // rows g and g + 8; l: this lane's columns
+    // ldmatrix lane addresses: A-like (rows (mi & 1) * 8 + r, columns + (mi >> 1) * 8) and B-like for the
+    // keys as n (rows (mi >> 1) * 8 + r, columns + (mi & 1) * 8)
     const int mi = lane >> 3, r8 = lane & 7;
     const int a_row = (mi & 1) * 8 + r8, a_col = (mi >> 1) * 8;
     const int b_row = (mi >> 1) * 8 + r8, b_col = (mi & 1) * 8;
@@ -137,102 +142,104 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
             asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();
-        // ---- S = Q K^T: this warp's m-tile (warp & 1) and keys (warp >> 1) * 16 .. + 15
+        // ---- S = Q K^T: 16 heads x 32 keys (four n8 tiles)
+        float s[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
         {
-            const int mt = warp & 1, n0 = (warp >> 1) * 16;
-            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
             const uint32_t qa = lat_smem(Qs + (mt * 16 + a_row) * LD + a_col);
-            const uint32_t ka = lat_smem(Ks + (n0 + b_row) * LD + b_col);
+            const uint32_t ka = lat_smem(Ks + b_row * LD + b_col);
+            const uint32_t kb16 = ka + 16 * LD * 2;                 // keys 16 .. 31
             for (int k0 = 0; k0 < p.W; k0 += 16) {
                 uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
                 lat_ldsm(qa + k0 * 2, a0, a1, a2, a3);
                 lat_ldsm(ka + k0 * 2, b0, b1, b2, b3);
                 lat_mma(s[0], a0, a1, a2, a3, b0, b1);
                 lat_mma(s[1], a0, a1, a2, a3, b2, b3);
-            }
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int row = mt * 16 + g + (e >> 1) * 8, col = n0 + j * 8 + 2 * t4 + (e & 1);
-                    float v = s[j][e] * p.scale;
-                    if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
-                    Ss[row * (LAT_TILE + 1) + col] = (kt + col < ke) ? v : -INFINITY;
-                }
-        }
-        __syncthreads();
-        // ---- softmax step: warp w owns heads 8w .. 8w + 7, a lane per key
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int row = warp * 8 + i;
-            const float v = Ss[row * (LAT_TILE + 1) + lane];
-            const float m_old = m_s[row];
-            const float m_new = fmaxf(m_old, warp_max(v));            // the tile's first key is always live
-            const float e = expf(v - m_new);                           // exp(-inf) = 0
-            const float sum = warp_sum(e);
-            Ps[row * (LAT_TILE + LAT_PAD) + lane] = __float2bfloat16_rn(e);
-            __syncwarp();
-            if (lane == 0) {
-                const float alpha = expf(m_old - m_new);               // 0 at the first tile
-                a_s[row] = alpha;
-                l_s[row] = l_s[row] * alpha + sum;
-                m_s[row] = m_new;
+                lat_ldsm(kb16 + k0 * 2, b0, b1, b2, b3);
+                lat_mma(s[2], a0, a1, a2, a3, b0, b1);
+                lat_mma(s[3], a0, a1, a2, a3, b2, b3);
             }
         }
-        __syncthreads();
-        // ---- O = O * alpha + P V over this warp's value columns
-        {
-            float al[2][2];
+        // ---- scale, cap, mask; softmax step in registers (a row's 32 scores lie in the four lanes of a quad)
+        float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) { al[mt][0] = a_s[mt * 16 + g]; al[mt][1] = a_s[mt * 16 + g + 8]; }
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
+            for (int e = 0; e < 4; ++e) {
+                float v = s[j][e] * p.scale;
+                if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
+                if (kt + j * 8 + 2 * t4 + (e & 1) >= ke) v = -INFINITY;
+                s[j][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        float alpha[2];
 #pragma unroll
-                for (int j = 0; j < LAT_MAX_NT; ++j) {
-                    acc[mt][j][0] *= al[mt][0]; acc[mt][j][1] *= al[mt][0];
-                    acc[mt][j][2] *= al[mt][1]; acc[mt][j][3] *= al[mt][1];
-                }
+        for (int x = 0; x < 2; ++x) {
+            mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 1));
+            mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 2));
+            const float m_new = fmaxf(m_run[x], mx[x]);                // finite: the tile's first key is live
+            alpha[x] = expf(m_run[x] - m_new);                         // 0 at the first tile
+            m_run[x] = m_new;
+        }
+        float sum[2] = {0.f, 0.f};
 #pragma unroll
-            for (int kk = 0; kk < LAT_TILE / 16; ++kk) {
-                uint32_t pa[2][4];
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-                    lat_ldsm(lat_smem(Ps + (mt * 16 + a_row) * (LAT_TILE + LAT_PAD) + kk * 16 + a_col), pa[mt][0],
-                             pa[mt][1], pa[mt][2], pa[mt][3]);
-                // V as the B operand (k = key, n = column): transposed 8x8 pieces of the key tile;
-                // matrices: (keys 0-7, cols 0-7), (keys 8-15, cols 0-7), (keys 0-7, cols 8-15), (keys 8-15, cols 8-15)
-                const uint32_t va = lat_smem(Ks + (kk * 16 + a_row) * LD + col0 + a_col);
+            for (int e = 0; e < 4; ++e) {
+                s[j][e] = expf(s[j][e] - m_run[e >> 1]);               // exp(-inf) = 0
+                sum[e >> 1] += s[j][e];
+            }
+        l_run[0] = l_run[0] * alpha[0] + sum[0];
+        l_run[1] = l_run[1] * alpha[1] + sum[1];
 #pragma unroll
-                for (int jp = 0; jp < LAT_MAX_NT / 2; ++jp) {
-                    if (2 * jp < nt_w) {
-                        uint32_t b0, b1, b2, b3;
-                        lat_ldsm_t(va + jp * 32, b0, b1, b2, b3);
+        for (int j = 0; j < LAT_MAX_NT; ++j) {
+            acc[j][0] *= alpha[0]; acc[j][1] *= alpha[0];
+            acc[j][2] *= alpha[1]; acc[j][3] *= alpha[1];
+        }
+        // ---- O += P V over this warp's half of the value columns; P from the score registers
 #pragma unroll
-                        for (int mt = 0; mt < 2; ++mt) {
-                            lat_mma(acc[mt][2 * jp], pa[mt][0], pa[mt][1], pa[mt][2], pa[mt][3], b0, b1);
-                            lat_mma(acc[mt][2 * jp + 1], pa[mt][0], pa[mt][1], pa[mt][2], pa[mt][3], b2, b3);
-                        }
-                    }
+        for (int kk = 0; kk < LAT_TILE / 16; ++kk) {
+            const uint32_t pa0 = lat_pack(s[2 * kk][0], s[2 * kk][1]), pa1 = lat_pack(s[2 * kk][2], s[2 * kk][3]);
+            const uint32_t pa2 = lat_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]), pa3 = lat_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            // V as the B operand (k = key, n = column): transposed 8x8 pieces of the key tile;
+            // matrices: (keys 0-7, cols 0-7), (keys 8-15, cols 0-7), (keys 0-7, cols 8-15), (keys 8-15, cols 8-15)
+            const uint32_t va = lat_smem(Ks + (kk * 16 + a_row) * LD + col0 + a_col);
+#pragma unroll
+            for (int jp = 0; jp < LAT_MAX_NT / 2; ++jp) {
+                if (2 * jp < nt_w) {
+                    uint32_t b0, b1, b2, b3;
+                    lat_ldsm_t(va + jp * 32, b0, b1, b2, b3);
+                    lat_mma(acc[2 * jp], pa0, pa1, pa2, pa3, b0, b1);
+                    lat_mma(acc[2 * jp + 1], pa0, pa1, pa2, pa3, b2, b3);
                 }
             }
         }
-        __syncthreads();                                            // the tile, S and P may be overwritten
+        __syncthreads();                                            // the tile's buffer may be written again
     }
     pdl_launch_dependents();
     // ---- this split's partial results
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        l_run[x] += __shfl_xor_sync(0xffffffffu, l_run[x], 1);
+        l_run[x] += __shfl_xor_sync(0xffffffffu, l_run[x], 2);
+    }
     float* po = p.part_o + part * LAT_HEADS * p.V;
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int j = 0; j < LAT_MAX_NT; ++j)
+        if (j < nt_w) {
+            const int c = col0 + j * 8 + 2 * t4;
+            *reinterpret_cast<float2*>(po + (size_t)(mt * 16 + g) * p.V + c) = make_float2(acc[j][0], acc[j][1]);
+            *reinterpret_cast<float2*>(po + (size_t)(mt * 16 + g + 8) * p.V + c) = make_float2(acc[j][2], acc[j][3]);
+        }
+    if (ch == 0 && t4 == 0) {
 #pragma unroll
-        for (int j = 0; j < LAT_MAX_NT; ++j)
-            if (j < nt_w) {
-                const int c = col0 + j * 8 + 2 * t4;
-                *reinterpret_cast<float2*>(po + (size_t)(mt * 16 + g) * p.V + c) = make_float2(acc[mt][j][0], acc[mt][j][1]);
-                *reinterpret_cast<float2*>(po + (size_t)(mt * 16 + g + 8) * p.V + c) = make_float2(acc[mt][j][2], acc[mt][j][3]);
-            }
-    if (tid < LAT_HEADS) {
-        p.part_ml[(part * LAT_HEADS + tid) * 2] = m_s[tid];
-        p.part_ml[(part * LAT_HEADS + tid) * 2 + 1] = l_s[tid];
+        for (int x = 0; x < 2; ++x) {
+            p.part_ml[(part * LAT_HEADS + mt * 16 + g + 8 * x) * 2] = m_run[x];
+            p.part_ml[(part * LAT_HEADS + mt * 16 + g + 8 * x) * 2 + 1] = l_run[x];
+        }
     }
 }
 
@@ -240,37 +247,54 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
 // the splits' weights exp(m_z - m) / l are worked out once, into shared memory (splits floats).
 __global__ void __launch_bounds__(128)
 latent_combine_kernel(const float* part_o, const float* part_ml, bf16* out, int H, int V, int chunks, int splits) {
-    extern __shared__ float wz[];
+    extern __shared__ float wz[];                                  // [splits] maxima, then weights
+    __shared__ float lz[128];                                       // sums of up to 128 splits a round
+    __shared__ float m_all, inv_all;
     pdl_wait();
     pdl_launch_dependents();
     const int tok = blockIdx.x, head = blockIdx.y;
     const int hc = head / LAT_HEADS, r = head % LAT_HEADS;
     const size_t base = ((size_t)tok * chunks + hc) * splits;
-    float m = -INFINITY;
-    for (int z = 0; z < splits; ++z) m = fmaxf(m, part_ml[((base + z) * LAT_HEADS + r) * 2]);
-    float l = 0.f;
-    for (int z = 0; z < splits; ++z) {
-        const float mz = part_ml[((base + z) * LAT_HEADS + r) * 2];
-        if (mz != -INFINITY) l += part_ml[((base + z) * LAT_HEADS + r) * 2 + 1] * expf(mz - m);
-    }
-    const float inv = 1.0f / l;
-    for (int z = threadIdx.x; z < splits; z += blockDim.x) {
-        const float mz = part_ml[((base + z) * LAT_HEADS + r) * 2];
-        wz[z] = mz != -INFINITY ? expf(mz - m) * inv : 0.f;
+    // all splits' maxima at once (one load a thread), then their common maximum and the weighted sum in split order
+    for (int z = threadIdx.x; z < splits; z += blockDim.x) wz[z] = part_ml[((base + z) * LAT_HEADS + r) * 2];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m = -INFINITY;
+        for (int z = 0; z < splits; ++z) m = fmaxf(m, wz[z]);
+        m_all = m;
     }
     __syncthreads();
+    const float m = m_all;
+    float l = 0.f;
+    for (int z0 = 0; z0 < splits; z0 += 128) {
+        const int z = z0 + threadIdx.x;
+        float e = 0.f, lv = 0.f;
+        if (z < splits && wz[z] != -INFINITY) {
+            e = expf(wz[z] - m);
+            lv = part_ml[((base + z) * LAT_HEADS + r) * 2 + 1] * e;
+        }
+        __syncthreads();
+        if (z < splits) wz[z] = e;
+        lz[threadIdx.x] = lv;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int i = 0; i < min(128, splits - z0); ++i) l += lz[i];
+        }
+    }
+    if (threadIdx.x == 0) inv_all = 1.0f / l;
+    __syncthreads();
+    const float inv = inv_all;
     for (int c = threadIdx.x; c < V; c += blockDim.x) {
         float o = 0.f;
         for (int z = 0; z < splits; ++z)
             if (wz[z] != 0.f) o += part_o[((base + z) * LAT_HEADS + r) * V + c] * wz[z];
-        out[((size_t)tok * H + head) * V + c] = __float2bfloat16_rn(o);
+        out[((size_t)tok * H + head) * V + c] = __float2bfloat16_rn(o * inv);
     }
 }
 
 // Shared memory of the attention kernel for key rows of W elements.
 static size_t latent_smem(int W) {
-    return (size_t)(LAT_HEADS + 2 * LAT_TILE) * (W + LAT_PAD) * 2 + (size_t)LAT_HEADS * (LAT_TILE + 1) * 4 +
-           (size_t)LAT_HEADS * (LAT_TILE + LAT_PAD) * 2 + 3 * LAT_HEADS * 4;
+    return (size_t)(LAT_HEADS + 2 * LAT_TILE) * (W + LAT_PAD) * 2;
 }
 
 // q [n, H * W], cache [pages, 1, bs, W], out [n, H * V] (all bfloat16); part_o needs n * chunks * n_splits
@@ -282,7 +306,7 @@ RLLM_API int rllm_latent_decode_attention(const void* q, const void* cache, void
                                           float softcap, int split_keys, int n_splits, long long n_pages, int* err,
                                           cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (H <= 0 || W % 16 || V % 64 || V <= 0 || V > 8 * LAT_MAX_NT * 4 || V > W || bs <= 0 || split_keys <= 0 ||
+    if (H <= 0 || W % 16 || V % 64 || V <= 0 || V > 16 * LAT_MAX_NT || V > W || bs <= 0 || split_keys <= 0 ||
         split_keys % LAT_TILE || n_splits <= 0 || n_splits > 8192 || !part_o || !part_ml || softcap < 0.f)
         return (int)cudaErrorInvalidValue;
     const size_t smem = latent_smem(W);
