@@ -91,11 +91,13 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
     const int* table = p.block_table + (size_t)p.seq_ids[tok] * p.table_stride;
     const int chunks = p.W / 8;                                     // 16-byte pieces of a row
     // queries of this chunk of heads; rows beyond H are zero
-    for (int i = tid; i < LAT_HEADS * chunks; i += 128) {
-        const int r = i / chunks, c = i - r * chunks;
-        const bool live = head0 + r < p.H;
-        const bf16* src = p.q + ((size_t)tok * p.H + (live ? head0 + r : 0)) * p.W + c * 8;
-        lat_cp16(lat_smem(Qs + r * LD + c * 8), src, live ? 16 : 0);
+    // (four threads a row, each every fourth 16-byte piece: one address computation a thread)
+    const int my_row = tid >> 2, my_c0 = tid & 3;
+    {
+        const bool live = head0 + my_row < p.H;
+        const bf16* src = p.q + ((size_t)tok * p.H + (live ? head0 + my_row : 0)) * p.W;
+        const uint32_t dst = lat_smem(Qs + my_row * LD);
+        for (int c = my_c0; c < chunks; c += 4) lat_cp16(dst + c * 16, src + c * 8, live ? 16 : 0);
     }
     // This warp: the 16 heads of m-tile `mt` against ALL keys of a tile (so a head's scores, its softmax
     // step and its P fragments stay in this warp's registers: the two warps of an m-tile compute the same
@@ -117,18 +119,17 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
 
     // a key tile on its way: rows first .. first + 31 of the request, zeros beyond ke; one cp.async group
     auto fetch_tile = [&](bf16* dst, int first) {
-        for (int i = tid; i < LAT_TILE * chunks; i += 128) {
-            const int r = i / chunks, c = i - r * chunks;
-            const int key = first + r;
-            const bool live = key < ke;
-            int page = live ? table[key / p.bs] : 0;
-            if ((unsigned)page >= (unsigned)p.n_pages) {
-                if (p.err) atomicExch(p.err, RLLM_ERR_PAGE);
-                page = 0;
-            }
-            const bf16* src = p.cache + ((size_t)page * p.bs + (live ? key % p.bs : 0)) * p.W + c * 8;
-            lat_cp16(lat_smem(dst + r * LD + c * 8), src, live ? 16 : 0);
+        // four threads a key row: one table look-up a thread and tile, then every fourth 16-byte piece of the row
+        const int key = first + my_row;
+        const bool live = key < ke;
+        int page = live ? table[key / p.bs] : 0;
+        if ((unsigned)page >= (unsigned)p.n_pages) {
+            if (p.err) atomicExch(p.err, RLLM_ERR_PAGE);
+            page = 0;
         }
+        const bf16* src = p.cache + ((size_t)page * p.bs + (live ? key % p.bs : 0)) * p.W;
+        const uint32_t d = lat_smem(dst + my_row * LD);
+        for (int c = my_c0; c < chunks; c += 4) lat_cp16(d + c * 16, src + c * 8, live ? 16 : 0);
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
     fetch_tile(Kbuf, kb);                                           // with the queries in the same group
@@ -286,8 +287,15 @@ latent_combine_kernel(const float* part_o, const float* part_ml, bf16* out, int 
     const float inv = inv_all;
     for (int c = threadIdx.x; c < V; c += blockDim.x) {
         float o = 0.f;
-        for (int z = 0; z < splits; ++z)
-            if (wz[z] != 0.f) o += part_o[((base + z) * LAT_HEADS + r) * V + c] * wz[z];
+        for (int z0 = 0; z0 < splits; z0 += 4) {                    // four splits' loads in flight, added in split order
+            float v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)                             // an empty split wrote no output: it is not read
+                v[i] = (z0 + i < splits && wz[z0 + i] != 0.f) ? part_o[((base + z0 + i) * LAT_HEADS + r) * V + c] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (z0 + i < splits) o += v[i] * wz[z0 + i];
+        }
         out[((size_t)tok * H + head) * V + c] = __float2bfloat16_rn(o * inv);
     }
 }
