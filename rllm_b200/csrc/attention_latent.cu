@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(const LatentParams p
 __global__ void __launch_bounds__(128)
 latent_combine_kernel(const float* part_o, const float* part_ml, bf16* out, int H, int V, int chunks, int splits) {
     extern __shared__ float wz[];                                  // [splits] maxima, then weights
-    __shared__ float lz[128];                                       // sums of up to 128 splits a round
+    __shared__ float lz[128];                                       // the sums of 128 splits at a time
     __shared__ float m_all, inv_all;
     pdl_wait();
     pdl_launch_dependents();
